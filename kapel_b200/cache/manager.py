@@ -32,11 +32,14 @@ from .pages import CacheFull, host_library
 
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values of `kv_heads` heads of `head_dim`; `window` None keeps every key."""
+    """Keys of `kv_heads` heads of `head_dim` and values of `v_head_dim` (None: the keys' size);
+    `window` None keeps every key, else the last `window` positions and the first `keep_first`."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    keep_first: int = 0
+    v_head_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -95,6 +98,7 @@ class CacheGroup:
             raise ValueError(f"a pool cannot have {n_pages} pages")
         self.needs = needs
         self.window = needs.window
+        self.keep_first = needs.keep_first if needs.window is not None else 0
         self.n_pages = n_pages
         self.layers: List[int] = []
         self.keys: Dict[int, object] = {}      # layer -> table [pages, kv_heads, page_size, head_dim]
@@ -102,8 +106,9 @@ class CacheGroup:
 
     @property
     def name(self) -> str:
-        w = "all" if self.window is None else f"window{self.window}"
-        return f"{w}/h{self.needs.kv_heads}/d{self.needs.head_dim}"
+        w = "all" if self.window is None else f"window{self.window}" + (f"+first{self.keep_first}" if self.keep_first else "")
+        v = "" if self.needs.v_head_dim in (None, self.needs.head_dim) else f"/v{self.needs.v_head_dim}"
+        return f"{w}/h{self.needs.kv_heads}/d{self.needs.head_dim}{v}"
 
 
 def _ptr(a: np.ndarray) -> int:
@@ -155,6 +160,9 @@ class CacheManager:
         self._h = self._lib.kc_create(n_groups, page_size, counts.ctypes.data_as(ip), windows.ctypes.data_as(ip), max_sequences)
         if not self._h:
             raise ValueError(f"a cache of {n_groups} groups, pages {counts.tolist()}, {max_sequences} sequences cannot be made")
+        for i, g in enumerate(self.groups):
+            if g.keep_first and self._lib.kc_set_keep_first(self._h, i, int(g.keep_first)) != 0:
+                raise ValueError(f"group {g.name}: {g.keep_first} first positions cannot be kept")
         self._scratch = np.zeros(max(n_groups, 1), np.int32)
         self._info = np.zeros(7, np.int64)
         self._info_ptr = self._info.ctypes.data
@@ -175,13 +183,15 @@ class CacheManager:
     # ------------------------------------------------------------------ device tables
     def allocate_tables(self, allocate: Callable, dtype) -> None:
         """Makes K and V tables [pages, kv_heads, page_size, head_dim] per layer (the keys of one kv
-        head in one page lie together, so a kernel fetches them in one piece), and state
+        head in one page lie together, so a kernel fetches them in one piece; the values' last
+        size is `v_head_dim` where a group gives one), and state
         tables [slots + 1, *shape]; they never move afterwards, so a recorded step stays valid."""
         for g in self.groups:
             shape = (max(g.n_pages, 1), g.needs.kv_heads, self.page_size, g.needs.head_dim)
+            v_shape = (*shape[:3], g.needs.v_head_dim or g.needs.head_dim)
             for layer in g.layers:
                 g.keys[layer] = allocate(shape, dtype)
-                g.values[layer] = allocate(shape, dtype)
+                g.values[layer] = allocate(v_shape, dtype)
         for layer, spec in self.state_specs.items():
             self.states[layer] = allocate((self.max_sequences + 1, *spec.shape), spec.dtype)
 

@@ -1,4 +1,5 @@
 """Typed configurations, the model-as-data records, and the architecture registry."""
+from .fusitar import FusitarConfig
 from .gemma2 import ConfigError, Gemma2Config
 from .registry import (
     architectures,
@@ -16,7 +17,9 @@ from .spec import (
     EmbedSpec,
     GatedMLPSpec,
     HeadSpec,
+    MLSTMSpec,
     ModelSpec,
+    MoESpec,
     NormSpec,
     PositionSpec,
     ScheduleEntry,

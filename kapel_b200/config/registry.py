@@ -12,6 +12,7 @@ import json
 from pathlib import Path
 from typing import Dict, Tuple
 
+from .fusitar import FusitarConfig
 from .gemma2 import ConfigError, Gemma2Config
 
 _ARCHITECTURES: Dict[str, type] = {}
@@ -35,11 +36,14 @@ def architectures() -> Tuple[str, ...]:
 
 
 def config_class_for(raw: dict):
-    """The class for a parsed config.json: `architectures[0]` first, then `model_type`."""
+    """The class for a parsed config.json: `architectures[0]` first, then `architecture` (a file
+    that names one only), then `model_type`."""
     names = []
     archs = raw.get("architectures")
     if isinstance(archs, list) and archs:
         names.append(archs[0])
+    if isinstance(raw.get("architecture"), str):
+        names.append(raw["architecture"])
     if raw.get("model_type") is not None:
         names.append(raw["model_type"])
     for n in names:
@@ -93,3 +97,4 @@ def read_config_file(name_or_path) -> dict:
 
 
 register_architecture(Gemma2Config, Gemma2Config.architecture, Gemma2Config.model_type)
+register_architecture(FusitarConfig, FusitarConfig.architecture, FusitarConfig.model_type)

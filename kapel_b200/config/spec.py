@@ -39,9 +39,12 @@ class PositionSpec:
 class AttentionSpec:
     """Grouped-query attention over a paged cache.
 
-    `window` None sees every key; else a query at position p sees keys j with p - j < window.
-    `scale` multiplies q.k; `softcap` c turns a score s into c*tanh(s/c) before the mask.
-    `weights` maps the roles q, k, v, o to tensor names, each [out, in].
+    `window` None sees every key; else a query at position p sees keys j with p - j < window,
+    and also the keys j < `keep_first` however far back. `scale` multiplies q.k; `softcap` c turns
+    a score s into c*tanh(s/c) before the mask. `weights` maps the roles q, k, v, o to tensor
+    names, each [out, in]; with `gated`, role g as well: the heads' outputs are multiplied by
+    sigmoid(g(h)) ahead of o. `v_head_dim` None: values have the keys' size. `q_norm` / `k_norm`:
+    a norm over the whole projection (all heads' rows at once) ahead of the split into heads.
     """
 
     hidden: int
@@ -54,6 +57,60 @@ class AttentionSpec:
     position: PositionSpec
     weights: Mapping[str, str]
     kind: str = "attention"
+    keep_first: int = 0
+    v_head_dim: Optional[int] = None
+    q_norm: Optional[NormSpec] = None
+    k_norm: Optional[NormSpec] = None
+    gated: bool = False
+
+
+@dataclass(frozen=True)
+class MLSTMSpec:
+    """A matrix memory with exponential gates (xLSTM's mLSTM), one state a head and request.
+
+    q (times head_dim^-1/2), k [heads, head_dim] and v [heads, v_head_dim] from the input; log input
+    gate cap*tanh(z_i/cap), log forget gate logsigmoid(cap*tanh(z_f/cap)) with z = W h + b per
+    head; memory S, normaliser n and running maximum m start at zero; the read-out S^T q is divided
+    by max(|n.q|, exp(-m)) + `floor`, then each head by its root mean square (`eps`), times the
+    weight `norm`, times sigmoid(g(h)), then o. `weights`: q, k, v, g, o, i, i_bias, f, f_bias, norm.
+    """
+
+    hidden: int
+    num_heads: int
+    head_dim: int
+    v_head_dim: int
+    gate_cap: float
+    eps: float
+    weights: Mapping[str, str]
+    floor: float = 1e-6
+    kind: str = "mlstm"
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    """A mixture of small feed-forwards: down(act(up(h))) for the `top` experts a token chooses,
+    added up with the router's weights.
+
+    Router scores s = `scoring`(router(h)); experts are chosen by s + the tensor `correction`
+    (where one is named) but weighted by s; with `groups` > 1 the experts form that many equal
+    groups of neighbours, a group scores the sum of its `group_top` best choice scores, and only
+    experts of the best `keep_groups` groups can be chosen; `renormalize` divides the chosen
+    weights by their sum. `weights`: router, correction (or absent), and the patterns `up` and
+    `down` with `{e}` for the expert's number.
+    """
+
+    hidden: int
+    experts: int
+    top: int
+    intermediate: int
+    activation: str                  # "relu2": the square of relu; or one of the gated unit's names
+    weights: Mapping[str, str]
+    groups: int = 1
+    keep_groups: int = 1
+    group_top: int = 2
+    scoring: str = "sigmoid"
+    renormalize: bool = False
+    kind: str = "moe"
 
 
 @dataclass(frozen=True)
@@ -72,7 +129,9 @@ class BlockSpec:
     """The arrangement of one layer.
 
     kind "sandwich": norms `pre_mixer`, `post_mixer`, `pre_ffn`, `post_ffn` around both
-    branches; kind "prenorm": `pre_mixer` and `pre_ffn` only.
+    branches; kind "prenorm": `pre_mixer` and `pre_ffn` only; kind "postnorm": the branches read
+    the residual itself and only their outputs are normed (`post_mixer`, `post_ffn`), and `ffn`
+    may be None for a layer without a feed-forward.
     """
 
     mixer: object

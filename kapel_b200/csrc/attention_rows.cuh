@@ -1,7 +1,8 @@
 // (shared by attention_f32.cu and attention_bf16.cu)
 // Attention over the paged cache, one query row at a time ("rows" kernels), for any element
 // type. A query row that has seen c positions (its own included) reads keys
-// [max(0, c - window), c) of its sequence through the block table; score = scale * q.k, then
+// [max(0, c - window), c) of its sequence through the block table, and with `keep` > 0 also the
+// keys [0, keep) that lie below its window; score = scale * q.k, then
 // cap * tanh(score / cap) if a cap is given, softmax over what it sees, weighted sum of values;
 // a row that sees nothing gives zeros. Scores, soft cap, softmax and sums are 32-bit.
 //
@@ -11,7 +12,9 @@
 // One block = one row x one kv head (a slice of up to GMAX of its query heads) x one chunk of
 // CHUNK key positions. Chunks are cut at absolute multiples of CHUNK, so what a row computes
 // does not depend on the rest of the batch. With more than one chunk slot the blocks write
-// (sum p.v, max, sum p) to scratch memory and `combine_kernel` merges them in chunk order.
+// (sum p.v, max, sum p) to scratch memory and `combine_kernel` merges them in slot order. The
+// first `keep_slots` slots are the kept first keys' chunks, the others the window's. Values may
+// have another size than keys (`dv`).
 #pragma once
 #include "common.cuh"
 
@@ -53,13 +56,31 @@ struct AttParams {
     const int* block_table;   // [entries, table_width]
     const int* row_entry;     // [rows]
     const int* row_count;     // [rows]
-    void* out;                // [rows, hq, d]
-    float* partial;           // [rows, hq, slots, d + 2] or null when slots == 1
+    void* out;                // [rows, hq, dv]
+    float* partial;           // [rows, hq, slots, dv + 2] or null when slots == 1
     int rows, hq, hkv, d, page_size, table_width, n_pages;
+    int dv;                   // the values' size (the v table is [pages, hkv, page_size, dv])
     int window;               // 0: none
-    int slots;                // chunk slots a row may touch
+    int keep;                 // with a window: the keys [0, keep) stay visible below it
+    int keep_slots;           // ceil(keep / CHUNK) with a window and keep > 0, else 0: the slots of those keys
+    int slots;                // chunk slots a row may touch, the kept keys' included
     float scale, cap;         // cap 0: none
 };
+
+// The keys [lo, hi) that slot z of a row with `count` positions holds (empty when hi <= lo): the
+// first `keep_slots` slots are chunks of the kept first keys below the window's start, the others
+// the window's chunks, counted from the chunk that holds its first key.
+__device__ __forceinline__ void slot_range(const AttParams& p, int count, int z, int& lo, int& hi) {
+    const int first = (p.window > 0 && count > p.window) ? count - p.window : 0;
+    if (z < p.keep_slots) {
+        lo = z * ATT_CHUNK;
+        hi = min(min(p.keep, first), (z + 1) * ATT_CHUNK);
+    } else {
+        const int chunk = first / ATT_CHUNK + (z - p.keep_slots);      // absolute chunk index
+        lo = max(first, chunk * ATT_CHUNK);
+        hi = min(count, (chunk + 1) * ATT_CHUNK);
+    }
+}
 
 // LPK: lanes that share one key (a power of two); VPL: 16-byte vectors of a key each lane holds.
 template <typename T, int GMAX, int LPK, int VPL>
@@ -77,19 +98,18 @@ rows_kernel(const AttParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     const int count = p.row_count[r];
-    const int first = (p.window > 0 && count > p.window) ? count - p.window : 0;
-    const int chunk = first / ATT_CHUNK + blockIdx.z;      // absolute chunk index
-    const int lo = max(first, chunk * ATT_CHUNK);
-    const int hi = min(count, (chunk + 1) * ATT_CHUNK);
+    int lo, hi;
+    slot_range(p, count, blockIdx.z, lo, hi);
     const int nkeys = hi - lo;
+    const int dv = p.dv;
     T* out = static_cast<T*>(p.out);
 
     if (nkeys <= 0) {
         // Nothing in this slot. The first slot of a row that sees nothing at all writes zeros.
         if (blockIdx.z == 0 && count <= 0)
             for (int g = 0; g < gn; ++g)
-                for (int i = tid; i < d; i += ATT_THREADS)
-                    Elem<T>::store(out + ((size_t)r * p.hq + kvh * group + g0 + g) * d + i, 0.f);
+                for (int i = tid; i < dv; i += ATT_THREADS)
+                    Elem<T>::store(out + ((size_t)r * p.hq + kvh * group + g0 + g) * dv + i, 0.f);
         return;
     }
 
@@ -174,7 +194,7 @@ rows_kernel(const AttParams p) {
     // ---- weighted sum of values: a thread owns two neighbouring components; thread groups of
     // d/2 share the keys when d/2 < ATT_THREADS, and add up in group order afterwards.
     const T* vt = static_cast<const T*>(p.v_table);
-    const int pairs = d / 2;
+    const int pairs = dv / 2;
     const int tgroups = pairs >= ATT_THREADS ? 1 : ATT_THREADS / pairs;
     const int tg = tid / pairs;                            // this thread's group (may be >= tgroups)
     float acc[GMAX][2];
@@ -186,7 +206,7 @@ rows_kernel(const AttParams p) {
             for (int j = jstart; j < nkeys; j += tgroups) {
                 const int line = sline[j];
                 if (line < 0) continue;
-                const T* vp = vt + kv_row(line, kvh, p.hkv, p.page_size) * d + 2 * pi;
+                const T* vp = vt + kv_row(line, kvh, p.hkv, p.page_size) * dv + 2 * pi;
                 const float v0 = Elem<T>::load(vp), v1 = Elem<T>::load(vp + 1);
 #pragma unroll
                 for (int g = 0; g < GMAX; ++g) {
@@ -203,8 +223,8 @@ rows_kernel(const AttParams p) {
 #pragma unroll
                 for (int g = 0; g < GMAX; ++g)
                     if (g < gn) {
-                        sacc[((size_t)tg * GMAX + g) * d + 2 * pi] = acc[g][0];
-                        sacc[((size_t)tg * GMAX + g) * d + 2 * pi + 1] = acc[g][1];
+                        sacc[((size_t)tg * GMAX + g) * dv + 2 * pi] = acc[g][0];
+                        sacc[((size_t)tg * GMAX + g) * dv + 2 * pi + 1] = acc[g][1];
                     }
             }
             __syncthreads();
@@ -213,8 +233,8 @@ rows_kernel(const AttParams p) {
                 for (int g = 0; g < GMAX; ++g)
                     if (g < gn)
                         for (int x = 1; x < tgroups; ++x) {
-                            acc[g][0] += sacc[((size_t)x * GMAX + g) * d + 2 * pi];
-                            acc[g][1] += sacc[((size_t)x * GMAX + g) * d + 2 * pi + 1];
+                            acc[g][0] += sacc[((size_t)x * GMAX + g) * dv + 2 * pi];
+                            acc[g][1] += sacc[((size_t)x * GMAX + g) * dv + 2 * pi + 1];
                         }
             }
         }
@@ -226,60 +246,69 @@ rows_kernel(const AttParams p) {
                 if (p.slots == 1) {
                     const float l = sstat[2 * g + 1];
                     const float inv = l > 0.f ? 1.f / l : 0.f;
-                    T* o = out + ((size_t)r * p.hq + h) * d + 2 * pi;
+                    T* o = out + ((size_t)r * p.hq + h) * dv + 2 * pi;
                     Elem<T>::store(o, acc[g][0] * inv);
                     Elem<T>::store(o + 1, acc[g][1] * inv);
                 } else {
-                    float* o = p.partial + (((size_t)r * p.hq + h) * p.slots + blockIdx.z) * (d + 2);
+                    float* o = p.partial + (((size_t)r * p.hq + h) * p.slots + blockIdx.z) * (dv + 2);
                     o[2 * pi] = acc[g][0];
                     o[2 * pi + 1] = acc[g][1];
-                    if (pi == 0) { o[d] = sstat[2 * g]; o[d + 1] = sstat[2 * g + 1]; }
+                    if (pi == 0) { o[dv] = sstat[2 * g]; o[dv + 1] = sstat[2 * g + 1]; }
                 }
             }
         }
     }
 }
 
-// out[r, h, :] = sum_z e^(m_z - M) acc_z / sum_z e^(m_z - M) l_z over the slots the row touched.
+// out[r, h, :] = sum_z e^(m_z - M) acc_z / sum_z e^(m_z - M) l_z over the slots that held keys of the row.
 template <typename T>
 __global__ void combine_kernel(const AttParams p) {
     const int r = blockIdx.x, h = blockIdx.y;
     const int count = p.row_count[r];
-    T* o = static_cast<T*>(p.out) + ((size_t)r * p.hq + h) * p.d;
+    const int dv = p.dv;
+    T* o = static_cast<T*>(p.out) + ((size_t)r * p.hq + h) * dv;
     if (count <= 0) return;                                // the rows kernel wrote zeros
-    const int first = (p.window > 0 && count > p.window) ? count - p.window : 0;
-    const int used = (count - 1) / ATT_CHUNK - first / ATT_CHUNK + 1;
-    const float* base = p.partial + ((size_t)r * p.hq + h) * p.slots * (p.d + 2);
+    const float* base = p.partial + ((size_t)r * p.hq + h) * p.slots * (dv + 2);
     float mx = -INFINITY;
-    for (int z = 0; z < used; ++z) mx = fmaxf(mx, base[(size_t)z * (p.d + 2) + p.d]);
+    for (int z = 0; z < p.slots; ++z) {
+        int lo, hi;
+        slot_range(p, count, z, lo, hi);
+        if (hi > lo) mx = fmaxf(mx, base[(size_t)z * (dv + 2) + dv]);
+    }
     float denom = 0.f;
-    for (int z = 0; z < used; ++z) {
-        const float m = base[(size_t)z * (p.d + 2) + p.d];
-        denom += (m == -INFINITY ? 0.f : soft_exp<T>(m - mx)) * base[(size_t)z * (p.d + 2) + p.d + 1];
+    for (int z = 0; z < p.slots; ++z) {
+        int lo, hi;
+        slot_range(p, count, z, lo, hi);
+        if (hi <= lo) continue;
+        const float m = base[(size_t)z * (dv + 2) + dv];
+        denom += (m == -INFINITY ? 0.f : soft_exp<T>(m - mx)) * base[(size_t)z * (dv + 2) + dv + 1];
     }
     const float inv = denom > 0.f ? 1.f / denom : 0.f;
-    for (int i = threadIdx.x; i < p.d; i += blockDim.x) {
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) {
         float acc = 0.f;
-        for (int z = 0; z < used; ++z) {
-            const float m = base[(size_t)z * (p.d + 2) + p.d];
+        for (int z = 0; z < p.slots; ++z) {
+            int lo, hi;
+            slot_range(p, count, z, lo, hi);
+            if (hi <= lo) continue;
+            const float m = base[(size_t)z * (dv + 2) + dv];
             const float w = m == -INFINITY ? 0.f : soft_exp<T>(m - mx);
-            acc = fmaf(w, base[(size_t)z * (p.d + 2) + i], acc);
+            acc = fmaf(w, base[(size_t)z * (dv + 2) + i], acc);
         }
         Elem<T>::store(o + i, acc * inv);
     }
 }
 
-static size_t rows_smem_bytes(int gmax, int d) {
-    const int pairs = d / 2;
+static size_t rows_smem_bytes(int gmax, int d, int dv) {
+    const int pairs = dv / 2;
     const int tgroups = pairs >= ATT_THREADS ? 1 : ATT_THREADS / pairs;
     size_t floats = (size_t)gmax * d + (size_t)gmax * ATT_CHUNK + ATT_CHUNK + 2 * gmax;
-    if (tgroups > 1) floats += (size_t)tgroups * gmax * d;
+    if (tgroups > 1) floats += (size_t)tgroups * gmax * dv;
     return floats * sizeof(float);
 }
 
 template <typename T, int GMAX, int LPK, int VPL>
 static int launch_rows(const AttParams& p, cudaStream_t s) {
-    const size_t smem = rows_smem_bytes(GMAX, p.d);
+    const size_t smem = rows_smem_bytes(GMAX, p.d, p.dv);
     if (smem > 48 * 1024) {
         if (smem > 200 * 1024) return fail("paged_attention: head_dim %d needs %zu bytes of shared memory", p.d, smem);
         cudaFuncSetAttribute(rows_kernel<T, GMAX, LPK, VPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -299,6 +328,7 @@ static int dispatch_lanes(const AttParams& p, cudaStream_t s) {
 #define KB_ATT(L, V) return launch_rows<T, GMAX, L, V>(p, s)
     if (vpl == 1) {
         switch (lpk) {
+            case 1: KB_ATT(1, 1);
             case 2: KB_ATT(2, 1);
             case 4: KB_ATT(4, 1);
             case 8: KB_ATT(8, 1);
@@ -307,6 +337,7 @@ static int dispatch_lanes(const AttParams& p, cudaStream_t s) {
         }
     } else if (vpl == 2) {
         switch (lpk) {
+            case 2: KB_ATT(2, 2);
             case 4: KB_ATT(4, 2);
             case 8: KB_ATT(8, 2);
             case 16: KB_ATT(16, 2);

@@ -74,6 +74,7 @@ struct Cache {
     int max_sequences = 0;
     std::vector<Pool> pools;
     std::vector<int> windows;              // -1: the group keeps every key
+    std::vector<int> kept_first;           // positions from 0 on that a group with a window keeps all the same
     std::vector<Seq> seqs;                 // by slot; slot 0 belongs to padding rows
     std::vector<int> free_slots;           // taken from the back
     long long released_pages = 0;
@@ -120,6 +121,7 @@ void* kc_create(int n_groups, int page_size, const int* pages, const int* window
     for (int g = 0; g < n_groups; ++g) {
         c->pools.emplace_back(pages[g]);
         c->windows.push_back(windows[g]);
+        c->kept_first.push_back(0);
     }
     c->seqs.resize((size_t)max_sequences + 1);
     for (int s = max_sequences; s >= 1; --s) c->free_slots.push_back(s);
@@ -127,6 +129,15 @@ void* kc_create(int n_groups, int page_size, const int* pages, const int* window
 }
 
 void kc_destroy(void* h) { delete as_cache(h); }
+
+// Group g's queries also read the first `keep_first` positions of their sequence, however far
+// back: the pages that hold them are never given back while the sequence lives.
+int kc_set_keep_first(void* h, int g, int keep_first) {
+    Cache* c = as_cache(h);
+    if (g < 0 || g >= c->groups() || keep_first < 0) return -1;
+    c->kept_first[(size_t)g] = keep_first;
+    return 0;
+}
 
 // A slot for a new sequence (1 ..), or -1 when none is free.
 int kc_add(void* h) {
@@ -318,7 +329,8 @@ long long kc_commit(void* h, int n, const int* slots, const int* counts) {
             if (first_needed <= 0) continue;
             std::vector<int>& pages = s->pages[(size_t)g];
             const int upto = (int)std::min<long long>(first_needed / c->page_size, (long long)pages.size());
-            for (int p = s->released[(size_t)g]; p < upto; ++p)
+            const int kept_pages = (c->kept_first[(size_t)g] + c->page_size - 1) / c->page_size;
+            for (int p = std::max(s->released[(size_t)g], kept_pages); p < upto; ++p)
                 if (pages[(size_t)p] >= 0) {
                     c->pools[(size_t)g].give(pages[(size_t)p]);
                     pages[(size_t)p] = -1;

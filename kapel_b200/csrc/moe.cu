@@ -1,0 +1,418 @@
+// A mixture of experts: the router, the lists of tokens by expert, the experts' two products as
+// grouped products over those lists, and the weighted sum.
+//
+//  route     z = router . h in 32-bit; s = sigmoid(z) (or softmax over the experts); choice scores
+//            s + correction; experts in equal groups of neighbours, a group's score the sum of its
+//            `group_top` largest choice scores, only the best `keep_groups` groups stay eligible;
+//            the `top` largest eligible choice scores are chosen (the lower number wins a tie) and
+//            weighted by s, optionally divided by their sum.
+//  sort      (token, k) pairs listed by expert, and the row tiles of the grouped products.
+//  product   out[pair] = act(A[row of pair] . W[expert of pair]^T): a block a (row tile of one
+//            expert, column tile); bfloat16 by mma.sync with 32-bit sums, float32 by FMA in
+//            ascending k. What a pair's row computes does not depend on its place in a tile.
+//  combine   out[token] = sum over k, in order, of weight[token, k] * y[token * top + k].
+#include "common.cuh"
+
+namespace kb {
+
+typedef __nv_bfloat16 bf16;
+
+// ------------------------------------------------------------------------------------------ route
+constexpr int ROUTE_THREADS = 128;
+
+template <typename TH>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, const float* __restrict__ correction,
+                 int* __restrict__ experts_out, float* __restrict__ weights_out, int width, int n_experts, int top, int groups,
+                 int keep_groups, int group_top, int softmax, int renormalize) {
+    extern __shared__ float sm[];
+    float* score = sm;                         // [E] s
+    float* choice = sm + n_experts;            // [E] s + correction
+    float* gscore = choice + n_experts;        // [groups]
+    int* state = reinterpret_cast<int*>(gscore + groups);   // [E] 0 eligible, 1 its group was dropped, 2 chosen
+    const int r = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const TH* hr = h + (size_t)r * width;
+    for (int x = warp; x < n_experts; x += ROUTE_THREADS / 32) {
+        const float* w = router + (size_t)x * width;
+        float acc = 0.f;
+        for (int i = lane; i < width; i += 32) acc = fmaf(Elem<TH>::load(hr + i), w[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) score[x] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    if (softmax) {
+        float mx = -INFINITY;
+        for (int x = 0; x < n_experts; ++x) mx = fmaxf(mx, score[x]);
+        float total = 0.f;
+        for (int x = 0; x < n_experts; ++x) { score[x] = expf(score[x] - mx); total += score[x]; }
+        for (int x = 0; x < n_experts; ++x) score[x] /= total;
+    } else {
+        for (int x = 0; x < n_experts; ++x) score[x] = 1.f / (1.f + expf(-score[x]));
+    }
+    for (int x = 0; x < n_experts; ++x) {
+        choice[x] = score[x] + (correction ? correction[x] : 0.f);
+        state[x] = 0;
+    }
+    const int per = n_experts / groups;
+    if (groups > 1 && keep_groups < groups) {
+        for (int g = 0; g < groups; ++g) {
+            // the sum of the group's `group_top` largest choice scores, by repeated selection
+            float total = 0.f;
+            int taken[8];
+            const int want = min(min(group_top, per), 8);
+            for (int t = 0; t < want; ++t) {
+                int best = -1;
+                float bv = -INFINITY;
+                for (int x = 0; x < per; ++x) {
+                    bool used = false;
+                    for (int u = 0; u < t; ++u) used |= taken[u] == x;
+                    if (used) continue;
+                    const float v = choice[g * per + x];
+                    if (best < 0 || v > bv) { best = x; bv = v; }
+                }
+                taken[t] = best;
+                total += bv;
+            }
+            gscore[g] = total;
+        }
+        // all but the best `keep_groups` groups lose their experts
+        for (int drop = 0; drop < groups - keep_groups; ++drop) {
+            int worst = -1;
+            float wv = INFINITY;
+            for (int g = groups - 1; g >= 0; --g) {          // among equals the higher number goes first
+                const float v = gscore[g];
+                if (v == INFINITY) continue;                 // already dropped
+                if (worst < 0 || v < wv) { worst = g; wv = v; }
+            }
+            if (worst < 0) break;
+            gscore[worst] = INFINITY;
+            for (int x = 0; x < per; ++x) state[worst * per + x] = 1;
+        }
+    }
+    float total = 0.f;
+    for (int t = 0; t < top; ++t) {
+        int best = -1;
+        float bv = -INFINITY;
+        for (int x = 0; x < n_experts; ++x) {
+            if (state[x] != 0) continue;
+            if (best < 0 || choice[x] > bv) { best = x; bv = choice[x]; }
+        }
+        if (best < 0)                                        // cannot happen with the sizes checked; stay in range all the same
+            for (int x = 0; x < n_experts && best < 0; ++x)
+                if (state[x] != 2) best = x;
+        if (best < 0) best = 0;
+        experts_out[(size_t)r * top + t] = best;
+        weights_out[(size_t)r * top + t] = score[best];
+        total += score[best];
+        state[best] = 2;
+    }
+    if (renormalize && total > 0.f)
+        for (int t = 0; t < top; ++t) weights_out[(size_t)r * top + t] /= total;
+}
+
+// ------------------------------------------------------------------------------------------- sort
+constexpr int GM = 32;         // rows of a grouped product's tile
+constexpr int SORT_THREADS = 1024;
+
+// One block. offsets [E + 1]; order [pairs]: pair numbers by expert (any order within an expert);
+// tile_expert / tile_first / tile_rows [tile_cap] and n_tiles[0].
+__global__ void __launch_bounds__(SORT_THREADS)
+moe_sort_kernel(const int* __restrict__ experts, int pairs, int n_experts, int* __restrict__ offsets, int* __restrict__ order,
+                int* __restrict__ tile_expert, int* __restrict__ tile_first, int* __restrict__ tile_rows, int* __restrict__ n_tiles,
+                int tile_cap) {
+    extern __shared__ int si[];
+    int* count = si;                 // [E]
+    int* cursor = si + n_experts;    // [E]
+    for (int x = threadIdx.x; x < n_experts; x += blockDim.x) count[x] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int x = experts[i];
+        if (x >= 0 && x < n_experts) atomicAdd(&count[x], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int x = 0; x < n_experts; ++x) {
+            offsets[x] = at;
+            cursor[x] = at;
+            for (int t = 0; t < count[x]; t += GM) {
+                if (tiles < tile_cap) {
+                    tile_expert[tiles] = x;
+                    tile_first[tiles] = at + t;
+                    tile_rows[tiles] = min(GM, count[x] - t);
+                }
+                ++tiles;
+            }
+            at += count[x];
+        }
+        offsets[n_experts] = at;
+        n_tiles[0] = min(tiles, tile_cap);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int x = experts[i];
+        if (x >= 0 && x < n_experts) order[atomicAdd(&cursor[x], 1)] = i;
+    }
+}
+
+// ---------------------------------------------------------------------------------------- product
+constexpr int GN = 64;         // columns of a tile
+constexpr int GK = 32;         // k step
+constexpr int GEMM_THREADS = 128;
+
+template <typename T> struct Acts;
+__device__ __forceinline__ float moe_act(float v, int act) {
+    if (act == 1) { const float r = fmaxf(v, 0.f); return r * r; }     // the square of relu
+    if (act == 2) return gelu_tanh(v);
+    if (act == 3) return silu(v);
+    return v;
+}
+
+struct GroupedParams {
+    const void* a;             // [*, k]: rows taken through `a_row`
+    const void* w;             // [experts, n, k]
+    void* out;                 // [pairs, n]: rows placed through `out_row`
+    const int* order;          // [pairs]: the pair at each sorted place
+    const int* tile_expert;
+    const int* tile_first;
+    const int* tile_rows;
+    const int* n_tiles;
+    int n, k, top, act;
+    int a_by;                  // 0: A's row is the sorted place; 1: the pair's token (pair / top)
+    int out_by;                // 0: the output row is the sorted place; 1: the pair number
+};
+
+// float32: each thread 4 rows x 4 columns, k ascending.
+__global__ void __launch_bounds__(GEMM_THREADS)
+moe_grouped_f32_kernel(const GroupedParams p) {
+    const int tile = blockIdx.x;
+    if (tile >= p.n_tiles[0]) return;
+    __shared__ float As[GK][GM + 1];
+    __shared__ float Ws[GK][GN + 1];
+    __shared__ int arow[GM], orow[GM];
+    const int expert = p.tile_expert[tile], first = p.tile_first[tile], nrows = p.tile_rows[tile];
+    const int n0 = blockIdx.y * GN;
+    const int tid = threadIdx.x;
+    if (tid < GM) {
+        const int place = first + min(tid, nrows - 1);
+        const int pair = p.order[place];
+        arow[tid] = p.a_by ? pair / p.top : place;
+        orow[tid] = p.out_by ? pair : place;
+    }
+    __syncthreads();
+    const float* A = static_cast<const float*>(p.a);
+    const float* W = static_cast<const float*>(p.w) + (size_t)expert * p.n * p.k;
+    const int tr = (tid / 16) * 4, tc = (tid % 16) * 4;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < p.k; k0 += GK) {
+        for (int i = tid; i < GM * GK; i += GEMM_THREADS) {
+            const int row = i / GK, kk = i % GK;
+            As[kk][row] = (k0 + kk < p.k) ? A[(size_t)arow[row] * p.k + k0 + kk] : 0.f;
+        }
+        for (int i = tid; i < GN * GK; i += GEMM_THREADS) {
+            const int col = i / GK, kk = i % GK;
+            Ws[kk][col] = (n0 + col < p.n && k0 + kk < p.k) ? W[(size_t)(n0 + col) * p.k + k0 + kk] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < GK; ++kk) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][tr + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = Ws[kk][tc + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    float* out = static_cast<float*>(p.out);
+    for (int i = 0; i < 4; ++i) {
+        if (tr + i >= nrows) continue;
+        for (int j = 0; j < 4; ++j)
+            if (n0 + tc + j < p.n) out[(size_t)orow[tr + i] * p.n + n0 + tc + j] = moe_act(acc[i][j], p.act);
+    }
+}
+
+// bfloat16 operands, 32-bit sums by mma.sync m16n8k16; four warps, each all 32 rows x 16 columns.
+template <typename TO>
+__global__ void __launch_bounds__(GEMM_THREADS)
+moe_grouped_bf16_kernel(const GroupedParams p) {
+    const int tile = blockIdx.x;
+    if (tile >= p.n_tiles[0]) return;
+    __shared__ __align__(16) bf16 As[GM][GK + 8];
+    __shared__ __align__(16) bf16 Ws[GN][GK + 8];
+    __shared__ int arow[GM], orow[GM];
+    const int expert = p.tile_expert[tile], first = p.tile_first[tile], nrows = p.tile_rows[tile];
+    const int n0 = blockIdx.y * GN;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < GM) {
+        const int place = first + min(tid, nrows - 1);
+        const int pair = p.order[place];
+        arow[tid] = p.a_by ? pair / p.top : place;
+        orow[tid] = p.out_by ? pair : place;
+    }
+    __syncthreads();
+    const bf16* A = static_cast<const bf16*>(p.a);
+    const bf16* W = static_cast<const bf16*>(p.w) + (size_t)expert * p.n * p.k;
+    const bool vec = (p.k % 8) == 0 && ((((uintptr_t)A) | ((uintptr_t)W)) & 15) == 0;
+    float acc[2][2][4] = {};
+    const int grp = lane >> 2, qd = lane & 3;
+    for (int k0 = 0; k0 < p.k; k0 += GK) {
+        if (vec) {
+            for (int i = tid; i < GM * (GK / 8); i += GEMM_THREADS) {
+                const int row = i / (GK / 8), kk = (i % (GK / 8)) * 8;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (k0 + kk < p.k) v = *reinterpret_cast<const uint4*>(A + (size_t)arow[row] * p.k + k0 + kk);
+                *reinterpret_cast<uint4*>(&As[row][kk]) = v;
+            }
+            for (int i = tid; i < GN * (GK / 8); i += GEMM_THREADS) {
+                const int col = i / (GK / 8), kk = (i % (GK / 8)) * 8;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (n0 + col < p.n && k0 + kk < p.k) v = *reinterpret_cast<const uint4*>(W + (size_t)(n0 + col) * p.k + k0 + kk);
+                *reinterpret_cast<uint4*>(&Ws[col][kk]) = v;
+            }
+        } else {
+            for (int i = tid; i < GM * GK; i += GEMM_THREADS) {
+                const int row = i / GK, kk = i % GK;
+                As[row][kk] = (k0 + kk < p.k) ? A[(size_t)arow[row] * p.k + k0 + kk] : __float2bfloat16_rn(0.f);
+            }
+            for (int i = tid; i < GN * GK; i += GEMM_THREADS) {
+                const int col = i / GK, kk = i % GK;
+                Ws[col][kk] = (n0 + col < p.n && k0 + kk < p.k) ? W[(size_t)(n0 + col) * p.k + k0 + kk] : __float2bfloat16_rn(0.f);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < GK; ks += 16) {
+            uint32_t af[2][4], bfr[2][2];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                const int r0 = mt * 16 + grp;
+                af[mt][0] = *reinterpret_cast<const uint32_t*>(&As[r0][ks + qd * 2]);
+                af[mt][1] = *reinterpret_cast<const uint32_t*>(&As[r0 + 8][ks + qd * 2]);
+                af[mt][2] = *reinterpret_cast<const uint32_t*>(&As[r0][ks + qd * 2 + 8]);
+                af[mt][3] = *reinterpret_cast<const uint32_t*>(&As[r0 + 8][ks + qd * 2 + 8]);
+            }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const int c0 = warp * 16 + nt * 8 + grp;
+                bfr[nt][0] = *reinterpret_cast<const uint32_t*>(&Ws[c0][ks + qd * 2]);
+                bfr[nt][1] = *reinterpret_cast<const uint32_t*>(&Ws[c0][ks + qd * 2 + 8]);
+            }
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+                    asm volatile(
+                        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                        : "+f"(acc[mt][nt][0]), "+f"(acc[mt][nt][1]), "+f"(acc[mt][nt][2]), "+f"(acc[mt][nt][3])
+                        : "r"(af[mt][0]), "r"(af[mt][1]), "r"(af[mt][2]), "r"(af[mt][3]), "r"(bfr[nt][0]), "r"(bfr[nt][1]));
+        }
+        __syncthreads();
+    }
+    TO* out = static_cast<TO*>(p.out);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const int row = mt * 16 + grp + (v >= 2 ? 8 : 0);
+                const int col = n0 + warp * 16 + nt * 8 + qd * 2 + (v & 1);
+                if (row < nrows && col < p.n) Elem<TO>::store(out + (size_t)orow[row] * p.n + col, moe_act(acc[mt][nt][v], p.act));
+            }
+}
+
+// ---------------------------------------------------------------------------------------- combine
+template <typename TO>
+__global__ void moe_combine_kernel(TO* __restrict__ out, const float* __restrict__ y, const float* __restrict__ weights,
+                                   long long rows, int width, int top) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * width) return;
+    const long long r = i / width;
+    const int c = (int)(i - r * width);
+    float acc = 0.f;
+    for (int t = 0; t < top; ++t) acc = fmaf(weights[r * top + t], y[((size_t)r * top + t) * width + c], acc);
+    Elem<TO>::store(out + i, acc);
+}
+
+}  // namespace kb
+
+using namespace kb;
+
+extern "C" int kb_moe_tile_rows() { return GM; }
+
+extern "C" int kb_moe_route(int* experts, float* weights, const void* h, int h_dt, const float* router, const float* correction,
+                            int rows, int width, int n_experts, int top, int groups, int keep_groups, int group_top,
+                            int softmax, int renormalize, void* stream) {
+    KB_REQUIRE(rows >= 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts, "moe_route: rows %d, width %d, %d experts, top %d", rows, width, n_experts, top);
+    KB_REQUIRE(groups >= 1 && n_experts % groups == 0 && keep_groups >= 1 && keep_groups <= groups,
+               "moe_route: %d experts in %d groups of which %d are kept", n_experts, groups, keep_groups);
+    KB_REQUIRE(keep_groups * (n_experts / groups) >= top, "moe_route: %d groups of %d experts cannot give %d", keep_groups, n_experts / groups, top);
+    KB_REQUIRE(group_top >= 1 && group_top <= 8, "moe_route: a group's score adds up %d scores (1 to 8)", group_top);
+    const size_t smem = ((size_t)3 * n_experts + groups) * sizeof(float);
+    KB_REQUIRE(smem <= 48 * 1024, "moe_route: %d experts are too many for the router's shared memory", n_experts);
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (h_dt == KB_DT_F32)
+        moe_route_kernel<float><<<rows, ROUTE_THREADS, smem, s>>>((const float*)h, router, correction, experts, weights, width, n_experts, top,
+                                                                  groups, keep_groups, group_top, softmax, renormalize);
+    else if (h_dt == KB_DT_BF16)
+        moe_route_kernel<bf16><<<rows, ROUTE_THREADS, smem, s>>>((const bf16*)h, router, correction, experts, weights, width, n_experts, top,
+                                                                 groups, keep_groups, group_top, softmax, renormalize);
+    else return fail("moe_route: dtype code %d is not known", h_dt);
+    return check_launch("moe_route");
+}
+
+extern "C" int kb_moe_sort(const int* experts, int pairs, int n_experts, int* offsets, int* order, int* tile_expert,
+                           int* tile_first, int* tile_rows, int* n_tiles, int tile_cap, void* stream) {
+    KB_REQUIRE(pairs >= 0 && n_experts > 0 && tile_cap >= 0, "moe_sort: %d pairs, %d experts", pairs, n_experts);
+    const size_t smem = (size_t)2 * n_experts * sizeof(int);
+    KB_REQUIRE(smem <= 48 * 1024, "moe_sort: %d experts are too many", n_experts);
+    moe_sort_kernel<<<1, SORT_THREADS, smem, (cudaStream_t)stream>>>(experts, pairs, n_experts, offsets, order, tile_expert, tile_first,
+                                                                    tile_rows, n_tiles, tile_cap);
+    return check_launch("moe_sort");
+}
+
+// act: 0 none, 1 relu squared, 2 gelu_tanh, 3 silu.
+extern "C" int kb_moe_grouped(void* out, int out_dt, const void* a, const void* w, int dt, const int* order, const int* tile_expert,
+                              const int* tile_first, const int* tile_rows, const int* n_tiles, int tile_cap, int n, int k, int top,
+                              int act, int a_by_token, int out_by_pair, void* stream) {
+    KB_REQUIRE(n > 0 && k > 0 && top > 0 && tile_cap >= 0, "moe_grouped: n %d, k %d, top %d", n, k, top);
+    KB_REQUIRE(act >= 0 && act <= 3, "moe_grouped: activation code %d is not known", act);
+    if (tile_cap == 0) return 0;
+    GroupedParams p;
+    p.a = a; p.w = w; p.out = out; p.order = order; p.tile_expert = tile_expert; p.tile_first = tile_first; p.tile_rows = tile_rows;
+    p.n_tiles = n_tiles; p.n = n; p.k = k; p.top = top; p.act = act; p.a_by = a_by_token; p.out_by = out_by_pair;
+    const int col_tiles = (n + GN - 1) / GN;
+    KB_REQUIRE(col_tiles <= 65535, "moe_grouped: %d columns are too many for one launch", n);
+    dim3 grid(tile_cap, col_tiles);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dt == KB_DT_F32) {
+        KB_REQUIRE(out_dt == KB_DT_F32, "moe_grouped: a 32-bit product writes 32-bit");
+        moe_grouped_f32_kernel<<<grid, GEMM_THREADS, 0, s>>>(p);
+    } else if (dt == KB_DT_BF16) {
+        if (out_dt == KB_DT_F32) moe_grouped_bf16_kernel<float><<<grid, GEMM_THREADS, 0, s>>>(p);
+        else if (out_dt == KB_DT_BF16) moe_grouped_bf16_kernel<bf16><<<grid, GEMM_THREADS, 0, s>>>(p);
+        else return fail("moe_grouped: output dtype code %d is not known", out_dt);
+    } else return fail("moe_grouped: dtype code %d is not known", dt);
+    return check_launch("moe_grouped");
+}
+
+extern "C" int kb_moe_combine(void* out, int out_dt, const float* y, const float* weights, long long rows, int width, int top,
+                              void* stream) {
+    KB_REQUIRE(rows >= 0 && width > 0 && top > 0, "moe_combine: rows %lld, width %d, top %d", rows, width, top);
+    if (rows == 0) return 0;
+    const long long blocks = (rows * width + 255) / 256;
+    KB_REQUIRE(blocks <= 0x7fffffffll, "moe_combine: too many rows for one launch");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dt == KB_DT_F32) moe_combine_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((float*)out, y, weights, rows, width, top);
+    else if (out_dt == KB_DT_BF16) moe_combine_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>((bf16*)out, y, weights, rows, width, top);
+    else return fail("moe_combine: output dtype code %d is not known", out_dt);
+    return check_launch("moe_combine");
+}

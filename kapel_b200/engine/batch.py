@@ -224,8 +224,9 @@ class StepBatch:
             self.memo[key] = (decode, tiles, split, slots, relative, host)
         return self.memo[key][:5]
 
-    def attention_slots(self, window: Optional[int]) -> int:
-        """Chunk slots the row-wise attention kernel needs for a layer with this window."""
+    def attention_slots(self, window: Optional[int], keep_first: int = 0) -> int:
+        """Chunk slots the row-wise attention kernel needs for a layer with this window; with
+        `keep_first` the slots of the kept first keys come on top."""
         if window not in self._slots_memo:
             if self.fixed_slots is not None:
                 n = self.fixed_slots
@@ -234,4 +235,13 @@ class StepBatch:
             else:
                 n = _chunks_touched(self.plan.row_count, window, self.chunk)
             self._slots_memo[window] = max(1, n)
-        return self._slots_memo[window]
+        extra = -(-keep_first // self.chunk) if (window and keep_first) else 0
+        return self._slots_memo[window] + extra
+
+    def entry_ranges(self):
+        """(start, end) on the device: rows [start[e], end[e]) are request e's. Made once a step."""
+        if "entry_ranges" not in self.memo:
+            from .. import kernels as K
+
+            self.memo["entry_ranges"] = K.entry_ranges(self.row_entry, self.entries)
+        return self.memo["entry_ranges"]

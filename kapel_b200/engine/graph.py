@@ -61,11 +61,20 @@ class StaticBatch:
         self._mma = {}
         self.h2d_bytes = self.total * 4
 
-    def attention_slots(self, window: Optional[int]) -> int:
+    def attention_slots(self, window: Optional[int], keep_first: int = 0) -> int:
         n = self.fixed_slots
         if window:
             n = min(n, (window - 1) // self.chunk + 2)
-        return max(1, n)
+        extra = -(-keep_first // self.chunk) if (window and keep_first) else 0
+        return max(1, n) + extra
+
+    def entry_ranges(self):
+        """(start, end) on the device: rows [start[e], end[e]) are request e's (here every row is its own)."""
+        if "entry_ranges" not in self.memo:
+            from .. import kernels as K
+
+            self.memo["entry_ranges"] = K.entry_ranges(self.row_entry, self.entries)
+        return self.memo["entry_ranges"]
 
     def attention_tiles(self, heads_per_kv: int, kv_heads: int, window: Optional[int] = None, head_dim: int = 256,
                         prompt_kernel: str = "mma"):
@@ -203,7 +212,11 @@ class DecodeGraphs:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                eng.model.forward(static, eng.cache)
+                kept = eng.save_states()                     # the eager run must not advance a mixer's own state
+                try:
+                    eng.model.forward(static, eng.cache)
+                finally:
+                    eng.restore_states(kept)
             torch.cuda.current_stream().wait_stream(side)
             graph = torch.cuda.CUDAGraph()
             static.memo.clear()
@@ -378,7 +391,11 @@ class PromptGraphs:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                eng.model.forward(static, eng.cache)        # once eagerly: attributes set, allocator warm, tiles planned
+                kept = eng.save_states()                     # the eager run must not advance a mixer's own state
+                try:
+                    eng.model.forward(static, eng.cache)    # once eagerly: attributes set, allocator warm, tiles planned
+                finally:
+                    eng.restore_states(kept)
             torch.cuda.current_stream().wait_stream(side)
             graph = torch.cuda.CUDAGraph()
             pool = self.pool or (self._pool_of.pool if self._pool_of is not None else None)

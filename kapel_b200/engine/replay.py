@@ -4,7 +4,7 @@ It samples nothing and owns nothing: it drives `Engine.step`, the step function 
 generation uses, with its cache and kernels. Kapel has no such program; the nearest are its
 parity checks (crates/kapel-models/examples/parity.rs:11-58, crates/kapel-models/tests/parity.rs:43-65).
 
-    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--max-requests R]
     trace_run --random CONFIG --seed-weights S --dtype ... --out DIR --max-tokens N
 
 `--random` takes the place of `--model`: a model of CONFIG (a config.json, or the name of one
@@ -36,9 +36,13 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="the folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="the most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+    ap.add_argument("--max-requests", type=int, default=4,
+                    help="the most requests that are live at any time: the cache has this many slots (default 4)")
     args = ap.parse_args(argv)
     if args.max_tokens <= 0:
         ap.error("--max-tokens must be positive")
+    if args.max_requests <= 0:
+        ap.error("--max-requests must be positive")
     if (args.model is None) == (args.random is None):
         ap.error("give either --model DIR or --random CONFIG")
 
@@ -52,9 +56,9 @@ def main(argv=None) -> int:
         from ..config import read_config_file
 
         engine = Engine.random(read_config_file(args.random), seed=args.seed_weights, dtype=args.dtype,
-                               max_tokens=args.max_tokens, max_sequences=16)
+                               max_tokens=args.max_tokens, max_sequences=args.max_requests)
     else:
-        engine = Engine.from_dir(args.model, dtype=args.dtype, max_tokens=args.max_tokens, max_sequences=16)
+        engine = Engine.from_dir(args.model, dtype=args.dtype, max_tokens=args.max_tokens, max_sequences=args.max_requests)
     print("trace_run: ready", file=sys.stderr, flush=True)
 
     for line in sys.stdin:

@@ -274,6 +274,15 @@ class Engine:
             K.fill_rows(table, slots, 0.0)
         self._fresh_slots_host = host          # pinned memory must outlive its copy
 
+    def save_states(self):
+        """Copies of the state tables (none when no part keeps a state): what a pass that is run
+        twice, once eagerly ahead of its recording and once as the recording, starts from both times."""
+        return {layer: table.clone() for layer, table in self.cache.states.items()}
+
+    def restore_states(self, kept) -> None:
+        for layer, table in kept.items():
+            self.cache.states[layer].copy_(table)
+
     @property
     def max_positions(self) -> Optional[int]:
         """The most positions a request may reach (config.json's max_position_embeddings), or None."""

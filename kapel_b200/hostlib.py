@@ -20,7 +20,7 @@ def host_library() -> ctypes.CDLL:
         sigs = {
             "kp_create": (vp, [i32]), "kp_destroy": (None, [vp]), "kp_take": (i32, [vp]), "kp_give": (i32, [vp, i32]),
             "kp_free": (i32, [vp]), "kp_is_held": (i32, [vp, i32]), "kp_check": (i32, [vp, ctypes.c_char_p, i32]),
-            "kc_create": (vp, [i32, i32, ip, ip, i32]), "kc_destroy": (None, [vp]), "kc_add": (i32, [vp]),
+            "kc_create": (vp, [i32, i32, ip, ip, i32]), "kc_destroy": (None, [vp]), "kc_set_keep_first": (i32, [vp, i32, i32]), "kc_add": (i32, [vp]),
             "kc_remove": (i32, [vp, i32]), "kc_length": (i32, [vp, i32]), "kc_free_slots": (i32, [vp]),
             "kc_released_pages": (i64, [vp]), "kc_free_pages": (None, [vp, ip]), "kc_held_pages": (i32, [vp, i32, ip]),
             "kc_pages_of": (i32, [vp, i32, i32, ip, i32]), "kc_pages_needed": (i32, [vp, i32, i32, ip]),

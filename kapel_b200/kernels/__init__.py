@@ -60,7 +60,8 @@ def library():
                 path = ensure_built()
                 lib = ctypes.CDLL(str(path))
                 lib.kb_last_error.restype = ctypes.c_char_p
-                for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats", "kb_sample_scratch_floats"):
+                for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats", "kb_sample_scratch_floats",
+                             "kb_mlstm_state_floats"):
                     getattr(lib, name).restype = ctypes.c_longlong
                 lib.kb_launch_count.restype = ctypes.c_ulonglong
                 lib.kb_set_pdl(1 if PDL else 0)
@@ -482,29 +483,37 @@ def attention_chunk() -> int:
 
 
 def paged_attention_rows(q, k_table, v_table, block_table, row_entry, row_count, page_size: int, window: Optional[int],
-                         scale: float, softcap: Optional[float], slots: int) -> torch.Tensor:
+                         scale: float, softcap: Optional[float], slots: int, keep_first: int = 0) -> torch.Tensor:
     """Attention of each query row over its sequence's pages; `slots` is the largest number of
-    key chunks (of `attention_chunk()` positions, cut at absolute multiples) any row touches."""
+    key chunks (of `attention_chunk()` positions, cut at absolute multiples) any row touches, plus,
+    with a window and `keep_first` > 0, the chunks of the first `keep_first` keys, which stay
+    visible below the window (`attention_keep_slots`). The values' size is the v table's last."""
     rows, hq, d = q.shape
     _need(q, "attention q")
     _need(k_table, "attention k table", q.dtype)
     _need(v_table, "attention v table", q.dtype)
-    if k_table.dim() != 4 or k_table.shape[2] != page_size or k_table.shape[3] != d or v_table.shape != k_table.shape:
-        raise KernelError(f"attention: tables {tuple(k_table.shape)} are not [pages, kv_heads, {page_size}, {d}]")
-    n_pages, hkv = k_table.shape[0], k_table.shape[1]
+    if k_table.dim() != 4 or k_table.shape[2] != page_size or k_table.shape[3] != d or v_table.dim() != 4 or v_table.shape[:3] != k_table.shape[:3]:
+        raise KernelError(f"attention: tables {tuple(k_table.shape)} / {tuple(v_table.shape)} are not [pages, kv_heads, {page_size}, {d}]")
+    n_pages, hkv, dv = k_table.shape[0], k_table.shape[1], v_table.shape[3]
     _need(block_table, "attention block table", torch.int32)
     _need(row_entry, "attention row_entry", torch.int32, (rows,))
     _need(row_count, "attention row_count", torch.int32, (rows,))
-    out = _fresh(q.shape, q.dtype, q.device)
+    out = _fresh((rows, hq, dv), q.dtype, q.device)
     lib = library()
-    need = lib.kb_paged_attention_scratch_floats(rows, hq, d, int(slots))
+    need = lib.kb_paged_attention_scratch_floats(rows, hq, dv, int(slots))
     scratch = _fresh((need,), torch.float32, q.device) if need else None
     _check(
         lib.kb_paged_attention_rows(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _dt(q, "attention q"), _ptr(block_table),
-                                    _ptr(row_entry), _ptr(row_count), rows, hq, hkv, d, int(page_size), int(block_table.shape[1]),
-                                    int(n_pages), int(window or 0), int(slots), _f(scale), _f(softcap or 0.0), _ptr(scratch), _stream())
+                                    _ptr(row_entry), _ptr(row_count), rows, hq, hkv, d, int(dv), int(page_size), int(block_table.shape[1]),
+                                    int(n_pages), int(window or 0), int(keep_first or 0), int(slots), _f(scale), _f(softcap or 0.0),
+                                    _ptr(scratch), _stream())
     )
     return out
+
+
+def attention_keep_slots(window: Optional[int], keep_first: int) -> int:
+    """Chunk slots the row-wise kernel spends on the kept first keys of a windowed layer."""
+    return -(-int(keep_first) // attention_chunk()) if (window and keep_first) else 0
 
 
 def attention_mma_rows(decode: bool) -> int:
@@ -648,6 +657,209 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
     return out
 
 
+# ------------------------------------------------------------------------------------------
+# Mixers whose roles share one stacked product: a role is a run of columns of each row.
+def _stacked(x, what: str):
+    """(tensor, dtype code, slices, stride, rows, row width) of a stacked product (a tensor or a SplitSum)."""
+    src, dt, splits, stride = _src(x, what)
+    rows, width = x.shape
+    return src, dt, splits, stride, int(rows), int(width)
+
+
+def proj_norm_append(stacked, q_off: int, k_off: int, v_off: int, q_norm, k_norm, lines, k_table, v_table, hq: int, hkv: int,
+                     d: int, dv: int, write_kv: bool, out_dtype: torch.dtype) -> torch.Tensor:
+    """q [rows, hq, d] from the columns q_off.. of `stacked`, normed over the whole projection when
+    `q_norm` = (weight [hq d], eps, offset) is given; the keys (normed by `k_norm` likewise) and the
+    values written at each row's line of the tables [pages, hkv, page_size, d] and [.., dv]."""
+    src, dt, splits, stride, rows, width = _stacked(stacked, "proj_norm_append input")
+    wq, eq, oq = q_norm if q_norm is not None else (None, 0.0, 0.0)
+    wk, ek, ok = k_norm if k_norm is not None else (None, 0.0, 0.0)
+    ws = [w for w in (wq, wk) if w is not None]
+    if len({w.dtype for w in ws}) > 1:
+        raise KernelError("proj_norm_append: the two norms' weights differ in dtype")
+    if wq is not None:
+        _need(wq, "proj_norm_append q norm", shape=(hq * d,))
+    if wk is not None:
+        _need(wk, "proj_norm_append k norm", shape=(hkv * d,))
+    w_dt = _dt(ws[0], "proj_norm_append norm") if ws else F32
+    q = _fresh((rows, hq, d), out_dtype, src.device)
+    table_lines, page_size = 0, 0
+    if write_kv:
+        _need(lines, "proj_norm_append lines", torch.int32, (rows,))
+        _need(k_table, "proj_norm_append k table", out_dtype)
+        _need(v_table, "proj_norm_append v table", out_dtype)
+        if k_table.dim() != 4 or k_table.shape[1] != hkv or k_table.shape[3] != d or v_table.dim() != 4 or \
+                tuple(v_table.shape) != (*k_table.shape[:3], dv):
+            raise KernelError(f"proj_norm_append: tables {tuple(k_table.shape)} / {tuple(v_table.shape)} are not [pages, {hkv}, page_size, {d} / {dv}]")
+        table_lines = k_table.shape[0] * k_table.shape[2]
+        page_size = k_table.shape[2]
+    _check(library().kb_proj_norm_append(
+        _ptr(src), dt, splits, ctypes.c_longlong(stride), width, int(q_off), int(k_off), int(v_off), _ptr(wq), _f(eq), _f(oq),
+        _ptr(wk), _f(ek), _f(ok), w_dt, _ptr(lines if write_kv else None), _ptr(q), _ptr(k_table if write_kv else None),
+        _ptr(v_table if write_kv else None), _CODES[out_dtype], rows, hq, hkv, d, dv, int(bool(write_kv)),
+        ctypes.c_longlong(table_lines), int(page_size), _stream()))
+    return q
+
+
+def head_gate(y: torch.Tensor, stacked, g_off: int, weight: Optional[torch.Tensor], unit: bool, eps: float,
+              out_dtype: torch.dtype) -> torch.Tensor:
+    """y [rows, heads, e] times sigmoid of the columns g_off.. of `stacked`; with `unit` each head is
+    first divided by its root mean square (eps inside the root); `weight` [heads e] multiplies too."""
+    _need(y, "head_gate input")
+    rows, heads, e = y.shape
+    src, dt, splits, stride, g_rows, width = _stacked(stacked, "head_gate gate")
+    if g_rows != rows:
+        raise KernelError(f"head_gate: {rows} rows against a gate of {g_rows}")
+    if weight is not None:
+        _need(weight, "head_gate weight", shape=(heads * e,))
+    out = _fresh((rows, heads, e), out_dtype, y.device)
+    _check(library().kb_head_gate(
+        _ptr(out), _CODES[out_dtype], _ptr(y), _dt(y, "head_gate input"), _ptr(src), dt, splits, ctypes.c_longlong(stride), width,
+        int(g_off), _ptr(weight), _dt(weight, "head_gate weight") if weight is not None else F32, int(bool(unit)), _f(eps),
+        ctypes.c_longlong(rows), heads, e, _stream()))
+    return out
+
+
+def entry_ranges(row_entry: torch.Tensor, entries: int):
+    """(start, end) int32 [entries]: rows [start[e], end[e]) are request e's in this step."""
+    _need(row_entry, "entry_ranges row_entry", torch.int32)
+    both = _fresh((2, max(int(entries), 1)), torch.int32, row_entry.device)
+    _check(library().kb_entry_ranges(_ptr(both[0]), _ptr(both[1]), _ptr(row_entry), int(row_entry.numel()), int(entries), _stream()))
+    return both[0], both[1]
+
+
+MLSTM_SLICE = 16          # value components a block of the scan kernel holds (the kernel file's MV)
+
+
+def mlstm_state_floats(d: int, e: int) -> int:
+    """Floats a head keeps between steps: the memory [d, e], and the normaliser [d] and the running
+    maximum once for every slice of value components the scan kernel cuts a head into. Plain
+    arithmetic (a cache is sized without the CUDA library); `mlstm_scan` checks it against the library's."""
+    return d * e + -(-e // MLSTM_SLICE) * (d + 1)
+
+
+def mlstm_scan(stacked, q_off: int, k_off: int, v_off: int, i_off: int, f_off: int, bias_i, bias_f, state, ranges, slots,
+               entries: int, heads: int, d: int, e: int, cap: float, q_scale: float, floor: float) -> torch.Tensor:
+    """The matrix memory's read-out [rows, heads, e] (float32, not yet normed) over the rows of a
+    step, request by request in row order, from and into `state` [slots, heads, state floats]."""
+    src, dt, splits, stride, rows, width = _stacked(stacked, "mlstm input")
+    _need(bias_i, "mlstm input-gate bias", torch.float32, (heads,))
+    _need(bias_f, "mlstm forget-gate bias", torch.float32, (heads,))
+    _need(state, "mlstm state", torch.float32)
+    per_head = mlstm_state_floats(d, e)
+    if state.dim() != 3 or state.shape[1] != heads or state.shape[2] != per_head:
+        raise KernelError(f"mlstm: a state table of {tuple(state.shape)}, expected [slots, {heads}, {per_head}]")
+    if int(library().kb_mlstm_state_floats(d, e)) != per_head:
+        raise KernelError("mlstm: the library cuts a head's state differently from the cache")
+    start, end = ranges
+    _need(start, "mlstm entry starts", torch.int32)
+    _need(end, "mlstm entry ends", torch.int32)
+    _need(slots, "mlstm slots", torch.int32)
+    if min(start.numel(), end.numel(), slots.numel()) < entries:
+        raise KernelError(f"mlstm: {entries} requests but ranges or slots for fewer")
+    out = _fresh((rows, heads, e), torch.float32, src.device)
+    _check(library().kb_mlstm_scan(
+        _ptr(out), _ptr(src), dt, splits, ctypes.c_longlong(stride), width, int(q_off), int(k_off), int(v_off), int(i_off), int(f_off),
+        _ptr(bias_i), _ptr(bias_f), _ptr(state), int(state.shape[0]), _ptr(start), _ptr(end), _ptr(slots), int(entries), rows,
+        heads, d, e, _f(cap), _f(q_scale), _f(floor), _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# Mixture of experts.
+MOE_ACT_CODES = {"none": 0, "relu2": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep_groups: int,
+              group_top: int, scoring: str, renormalize: bool):
+    """(experts int32 [rows, top], weights float32 [rows, top]) of each row of h [rows, width];
+    the router [experts, width] and the correction [experts] are float32."""
+    _need(h, "moe_route input")
+    rows, width = h.shape
+    _need(router, "moe_route router", torch.float32)
+    n_experts = router.shape[0]
+    if router.shape[1] != width:
+        raise KernelError(f"moe_route: router {tuple(router.shape)} against rows of {width}")
+    if correction is not None:
+        _need(correction, "moe_route correction", torch.float32, (n_experts,))
+    if scoring not in ("sigmoid", "softmax"):
+        raise KernelError(f"moe_route: scoring {scoring!r} is not known")
+    experts = _fresh((rows, top), torch.int32, h.device)
+    weights = _fresh((rows, top), torch.float32, h.device)
+    _check(library().kb_moe_route(_ptr(experts), _ptr(weights), _ptr(h), _dt(h, "moe_route input"), _ptr(router), _ptr(correction),
+                                  rows, width, n_experts, int(top), int(groups), int(keep_groups), int(group_top),
+                                  int(scoring == "softmax"), int(bool(renormalize)), _stream()))
+    return experts, weights
+
+
+_MOE_TILE_ROWS = None
+
+
+def moe_tile_rows() -> int:
+    global _MOE_TILE_ROWS
+    if _MOE_TILE_ROWS is None:
+        _MOE_TILE_ROWS = int(library().kb_moe_tile_rows())
+    return _MOE_TILE_ROWS
+
+
+class ExpertLists:
+    """The (token, k) pairs of a step listed by expert, and the row tiles of the grouped products."""
+
+    __slots__ = ("order", "offsets", "tiles", "tile_cap", "pairs", "top")
+
+
+def moe_sort(experts: torch.Tensor, n_experts: int) -> ExpertLists:
+    _need(experts, "moe_sort experts", torch.int32)
+    rows, top = experts.shape
+    pairs = rows * top
+    lists = ExpertLists()
+    lists.pairs, lists.top = pairs, top
+    # every expert's list ends with at most one tile that is not full
+    lists.tile_cap = pairs // moe_tile_rows() + min(n_experts, pairs)
+    buf = _fresh((n_experts + 1 + pairs + 3 * max(lists.tile_cap, 1) + 1,), torch.int32, experts.device)
+    at = n_experts + 1
+    lists.offsets, lists.order = buf[:at], buf[at : at + pairs]
+    at += pairs
+    cap = max(lists.tile_cap, 1)
+    lists.tiles = (buf[at : at + cap], buf[at + cap : at + 2 * cap], buf[at + 2 * cap : at + 3 * cap], buf[at + 3 * cap :])
+    _check(library().kb_moe_sort(_ptr(experts), pairs, int(n_experts), _ptr(lists.offsets), _ptr(lists.order), _ptr(lists.tiles[0]),
+                                 _ptr(lists.tiles[1]), _ptr(lists.tiles[2]), _ptr(lists.tiles[3]), int(lists.tile_cap), _stream()))
+    return lists
+
+
+def moe_grouped(a: torch.Tensor, w: torch.Tensor, lists: ExpertLists, act: str, a_by_token: bool, out_by_pair: bool,
+                out_dtype: torch.dtype) -> torch.Tensor:
+    """out [pairs, n]: act(a[row] . w[expert]^T) for every (token, k) pair, by expert. `a` rows are
+    taken by the pair's token (`a_by_token`) or by its place in the expert lists; the result's rows
+    are placed by pair number (`out_by_pair`) or by that place. w is [experts, n, k]."""
+    _need(a, "moe_grouped input")
+    _need(w, "moe_grouped weights", a.dtype)
+    if w.dim() != 3 or w.shape[2] != a.shape[1]:
+        raise KernelError(f"moe_grouped: weights {tuple(w.shape)} against rows of {a.shape[1]}")
+    if act not in MOE_ACT_CODES:
+        raise KernelError(f"moe_grouped: activation {act!r} is not known")
+    n, k = int(w.shape[1]), int(w.shape[2])
+    out = _fresh((lists.pairs, n), out_dtype, a.device)
+    t = lists.tiles
+    _check(library().kb_moe_grouped(_ptr(out), _CODES[out_dtype], _ptr(a), _ptr(w), _dt(a, "moe_grouped input"), _ptr(lists.order),
+                                    _ptr(t[0]), _ptr(t[1]), _ptr(t[2]), _ptr(t[3]), int(lists.tile_cap), n, k, int(lists.top),
+                                    MOE_ACT_CODES[act], int(bool(a_by_token)), int(bool(out_by_pair)), _stream()))
+    return out
+
+
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """out[token] = sum over k, in order, of weights[token, k] * y[token * top + k]."""
+    _need(y, "moe_combine input", torch.float32)
+    _need(weights, "moe_combine weights", torch.float32)
+    rows, top = weights.shape
+    width = y.shape[1]
+    if y.shape[0] != rows * top:
+        raise KernelError(f"moe_combine: {y.shape[0]} rows for {rows} tokens of {top} experts")
+    out = _fresh((rows, width), out_dtype, y.device)
+    _check(library().kb_moe_combine(_ptr(out), _CODES[out_dtype], _ptr(y), _ptr(weights), ctypes.c_longlong(rows), int(width), int(top), _stream()))
+    return out
+
+
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, uniform: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token a row: the first largest logit where temperature <= 0 (or none is given), else
     a draw with the row's uniform number."""
@@ -669,7 +881,8 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, uni
 # (crates/kapel-cli/examples/profile.rs:17-56): every entry point above is bracketed by CUDA
 # events and its device time added up under its name and its largest argument's shape.
 _TIMED = ("embed", "rope_table", "rope_append", "glu", "cast", "gather_rows", "rmsnorm", "add_rmsnorm", "gemm",
-          "paged_attention_rows", "paged_attention_mma", "sample")
+          "paged_attention_rows", "paged_attention_mma", "sample", "proj_norm_append", "head_gate", "mlstm_scan", "moe_route",
+          "moe_sort", "moe_grouped", "moe_combine")
 _timing = None
 _originals = {}
 

@@ -1,9 +1,11 @@
 """Layer parts: mixers, feed-forwards, norms, position encodings, blocks, and the two ends."""
 from .attention import Attention
 from .base import BuildContext, LayerCache, Part, linear, matrix_for, matrix_named, require_product_widths, stack_rows
-from .block import PreNormBlock, SandwichBlock
+from .block import PostNormBlock, PreNormBlock, SandwichBlock
 from .embedding import Embedding, VocabHead
 from .feed_forward import GatedMLP
+from .mlstm import MLSTM
+from .moe import MoE
 from .norm import RMSNorm, add_branch
 from .position import NoPosition, Rope
 from .registry import (
@@ -19,12 +21,15 @@ from .registry import (
 )
 
 register_part("mixer", "attention", Attention)
+register_part("mixer", "mlstm", MLSTM)
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "moe", MoE)
 register_part("norm", "rms", RMSNorm)
 register_part("position", "rope", Rope)
 register_part("position", "none", NoPosition)
 register_part("block", "sandwich", SandwichBlock)
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "postnorm", PostNormBlock)
 register_part("embedding", "embedding", Embedding)
 register_part("head", "vocab_head", VocabHead)
 

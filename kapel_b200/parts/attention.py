@@ -5,6 +5,12 @@ q, k, v come from one stacked product (Kapel stacks them at load: crates/kapel-m
 (Kapel: rope_any twice and write_rows_any twice, model.rs:1561-1579); attention reads the pages
 through the block table with scale, soft cap and window as arguments (model.rs:1580-1590);
 then the output product (model.rs:1633-1637).
+
+A spec may ask for more than that: a norm over the whole query and key projections, values of
+another size than keys, first keys that stay visible below the window, a sigmoid gate on the
+heads' outputs. Such a layer runs the general path: one stacked product q|k|v|g in 32-bit, one
+kernel that norms q and k and appends k and v to the cache, the row-wise attention kernel (which
+knows the kept first keys and the values' size), the gate, the output product.
 """
 from __future__ import annotations
 
@@ -21,31 +27,78 @@ class Attention(Part):
 
     @staticmethod
     def expected_tensors(spec):
+        dv = spec.v_head_dim or spec.head_dim
         qd, kvd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
         w = spec.weights
-        return {w["q"]: (qd, spec.hidden), w["k"]: (kvd, spec.hidden), w["v"]: (kvd, spec.hidden), w["o"]: (spec.hidden, qd)}
+        out = {w["q"]: (qd, spec.hidden), w["k"]: (kvd, spec.hidden), w["v"]: (spec.num_kv_heads * dv, spec.hidden),
+               w["o"]: (spec.hidden, spec.num_heads * dv)}
+        if spec.gated:
+            out[w["g"]] = (spec.num_heads * dv, spec.hidden)
+        for n in (spec.q_norm, spec.k_norm):
+            if n is not None:
+                out[n.weight] = (n.width,)
+        return out
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError(f"attention: {spec.num_heads} heads over {spec.num_kv_heads} kv heads")
-        if spec.head_dim % 16:
-            raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16 for the kernels")
+        self.v_dim = spec.v_head_dim or spec.head_dim
+        self.general = bool(spec.gated or spec.q_norm or spec.k_norm or spec.keep_first or self.v_dim != spec.head_dim)
+        piece = 16 if not self.general else (4 if ctx.is_f32 else 8)
+        if spec.head_dim % piece:
+            raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of {piece} for the kernels")
+        if self.v_dim % 2:
+            raise ValueError(f"attention: the values' size {self.v_dim} must be even for the kernels")
+        if spec.keep_first < 0 or (spec.keep_first and not spec.window):
+            raise ValueError(f"attention: {spec.keep_first} first keys kept with window {spec.window}")
+        for n, width in ((spec.q_norm, spec.num_heads * spec.head_dim), (spec.k_norm, spec.num_kv_heads * spec.head_dim)):
+            if n is not None and (n.kind != "rms" or n.width != width):
+                raise ValueError(f"attention: a norm over the whole projection must be an RMS norm of width {width}")
         require_product_widths(ctx, "attention", hidden_size=spec.hidden,
-                               **{"num_attention_heads x head_dim": spec.num_heads * spec.head_dim})
+                               **{"num_attention_heads x value size": spec.num_heads * self.v_dim})
         self.position = build_part("position", spec.position, ctx)
+        if self.general and self.position.rotary_dim:
+            raise ValueError("attention: a rotation together with projection norms, a gate, kept first keys or another value size is not built")
 
     def load(self, tensors):
         w = self.spec.weights
-        self.w_qkv = stack_rows(self.ctx, tensors, [w["q"], w["k"], w["v"]], "attention")
+        names = [w["q"], w["k"], w["v"]] + ([w["g"]] if self.spec.gated else [])
+        self.w_qkv = stack_rows(self.ctx, tensors, names, "attention")
         self.w_o = matrix_named(self.ctx, tensors, w["o"])
+        self.proj_norms = []
+        for n in (self.spec.q_norm, self.spec.k_norm):
+            if n is None:
+                self.proj_norms.append(None)
+                continue
+            t = tensors[n.weight]
+            t = t.to(self.ctx.device) if t.device != self.ctx.device else t
+            self.proj_norms.append((t.float() if self.ctx.is_f32 else t.contiguous(), n.eps, n.offset))
 
     def cache_needs(self) -> CacheNeeds:
         s = self.spec
-        return CacheNeeds(paged=PagedKV(s.num_kv_heads, s.head_dim, s.window))
+        return CacheNeeds(paged=PagedKV(s.num_kv_heads, s.head_dim, s.window, s.keep_first if s.window else 0,
+                                        self.v_dim if self.v_dim != s.head_dim else None))
+
+    def forward_general(self, h, batch, cache):
+        s, dv = self.spec, self.v_dim
+        nq, nk = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        stacked = linear(self.ctx, h, self.w_qkv, out_dtype=torch.float32, keep_split=True)
+        k_table, v_table = cache.tables()
+        group = batch.groups[cache.group]
+        q = K.proj_norm_append(stacked, 0, nq, nq + nk, self.proj_norms[0], self.proj_norms[1], group.lines, k_table, v_table,
+                               s.num_heads, s.num_kv_heads, s.head_dim, dv, cache.owns, self.ctx.dtype)
+        y = K.paged_attention_rows(
+            q, k_table, v_table, group.block_table, batch.row_entry, batch.row_count, self.ctx.page_size, s.window, s.scale,
+            s.softcap, batch.attention_slots(s.window, s.keep_first), s.keep_first)
+        if s.gated:
+            y = K.head_gate(y, stacked, nq + nk + s.num_kv_heads * dv, None, False, 0.0, self.ctx.dtype)
+        return linear(self.ctx, y.view(y.shape[0], s.num_heads * dv), self.w_o, keep_split=True)
 
     def forward(self, h, batch, cache):
         s = self.spec
+        if self.general:
+            return self.forward_general(h, batch, cache)
         qkv = linear(self.ctx, h, self.w_qkv, keep_split=True)
         k_table, v_table = cache.tables()
         group = batch.groups[cache.group]

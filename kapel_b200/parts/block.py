@@ -3,12 +3,16 @@
 "sandwich" (Gemma 2; crates/kapel-models/src/model.rs:1401-1460):
     h = pre_mixer(x); a = mixer(h); x += post_mixer(a); h = pre_ffn(x); m = ffn(h); x += post_ffn(m)
 "prenorm": the same without the post norms.
+"postnorm": the branches read the residual itself (rounded to the activation dtype), and only their
+    outputs are normed: x += post_mixer(mixer(x)); x += post_ffn(ffn(x)); a layer may have no
+    feed-forward.
 
 The residual x is float32 and is updated in place. Each sum is one kernel together with the
 norm before it and the norm after it, when those are RMS norms.
 """
 from __future__ import annotations
 
+from .. import kernels as K
 from .base import Part
 from .norm import add_branch
 from .registry import build_part
@@ -69,3 +73,63 @@ class SandwichBlock(Part):
 
 class PreNormBlock(SandwichBlock):
     norm_roles = ("pre_mixer", "pre_ffn")
+
+
+class PostNormBlock(Part):
+    """Each branch reads the residual and is normed on its way back into it."""
+
+    @classmethod
+    def expected_tensors(cls, spec):
+        from .registry import part_class
+
+        out = {}
+        out.update(part_class("mixer", spec.mixer.kind).expected_tensors(spec.mixer))
+        if spec.ffn is not None:
+            out.update(part_class("feed_forward", spec.ffn.kind).expected_tensors(spec.ffn))
+        for role in cls.roles_of(spec):
+            n = spec.norms[role]
+            out.update(part_class("norm", n.kind).expected_tensors(n))
+        return out
+
+    @staticmethod
+    def roles_of(spec):
+        return ("post_mixer", "post_ffn") if spec.ffn is not None else ("post_mixer",)
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        missing = [r for r in self.roles_of(spec) if r not in spec.norms]
+        if missing:
+            raise ValueError(f"{spec.kind} block: norms {missing} are missing")
+        self.mixer = build_part("mixer", spec.mixer, ctx)
+        self.ffn = build_part("feed_forward", spec.ffn, ctx) if spec.ffn is not None else None
+        self.norms = {r: build_part("norm", spec.norms[r], ctx) for r in self.roles_of(spec)}
+
+    @property
+    def graph_safe(self) -> bool:
+        parts = [self.mixer, *self.norms.values()] + ([self.ffn] if self.ffn is not None else [])
+        return all(p.graph_safe for p in parts)
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def first_norm(self):
+        return None                     # the mixer reads the residual as it is
+
+    def load(self, tensors):
+        self.mixer.load(tensors)
+        if self.ffn is not None:
+            self.ffn.load(tensors)
+        for n in self.norms.values():
+            n.load(tensors)
+
+    def _read(self, x):
+        return x if self.ctx.is_f32 else K.cast(x, self.ctx.dtype)
+
+    def forward(self, x, h, batch, cache, next_norm):
+        a = self.mixer.forward(self._read(x), batch, cache)
+        add_branch(self.ctx, x, a, self.norms["post_mixer"], None)
+        if self.ffn is None:
+            return x, (next_norm.forward(x) if next_norm is not None else None)
+        m = self.ffn.forward(self._read(x))
+        h_next = add_branch(self.ctx, x, m, self.norms["post_ffn"], next_norm)
+        return x, h_next

@@ -165,8 +165,9 @@ class _Sequence:
 
 
 class PlainCacheGroup:
-    def __init__(self, window: Optional[int], n_pages: int):
+    def __init__(self, window: Optional[int], n_pages: int, keep_first: int = 0):
         self.window = window
+        self.keep_first = keep_first       # a windowed group keeps the pages of its first positions
         self.pool = PlainPagePool(n_pages)
 
     @property
@@ -175,14 +176,15 @@ class PlainCacheGroup:
 
 
 class PlainCacheManager:
-    """`groups` is [(window or None, pages of the pool)], one entry a group of layers."""
+    """`groups` is [(window or None, pages of the pool)] or [(window, pages, first positions kept)],
+    one entry a group of layers."""
 
     def __init__(self, groups: Sequence[Tuple[Optional[int], int]], page_size: int, max_sequences: int):
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = page_size
         self.max_sequences = max_sequences
-        self.groups: List[PlainCacheGroup] = [PlainCacheGroup(w, n) for w, n in groups]
+        self.groups: List[PlainCacheGroup] = [PlainCacheGroup(*g) for g in groups]
         self._sequences: Dict[Hashable, _Sequence] = {}
         self._free_slots = list(range(max_sequences, 0, -1))     # slot 0 is the padding rows'
         self.released_pages = 0
@@ -346,7 +348,8 @@ class PlainCacheManager:
                 if first_needed <= 0:
                     continue
                 upto = min(first_needed // self.page_size, len(seq.pages[g]))
-                for p in range(seq.released[g], upto):
+                kept_pages = -(-group.keep_first // self.page_size)
+                for p in range(max(seq.released[g], kept_pages), upto):
                     if seq.pages[g][p] >= 0:
                         group.pool.give(seq.pages[g][p])
                         seq.pages[g][p] = -1

@@ -58,7 +58,7 @@ def test_steps_in_done_lines_and_files_out(monkeypatch, tmp_path, capsys):
     printed = capsys.readouterr()
     assert printed.out.split("\n")[:4] == ["done 0", "done 1", "done 2", "done 7"]       # nothing else on standard output
     eng = StandInEngine.made[-1]
-    assert eng.args == ("DIR", "float32", 128, 16)
+    assert eng.args == ("DIR", "float32", 128, 4)                                         # four slots unless --max-requests says otherwise
     assert eng.ended == ["a", "b"]
     assert sorted(p.name for p in out.iterdir()) == ["0.f32", "2.f32"]                   # steps 1 and 7 want nothing
     first = np.frombuffer((out / "0.f32").read_bytes(), dtype="<f4").reshape(-1, VOCAB)
