@@ -1,6 +1,7 @@
 """Throughput of the engine at Gemma 2 sizes with random weights, on one GPU.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--size 2b|9b|27b] [--layers L] [--impl reference]
+    python bench.py --design fusitar [--design-sizes s,m]      (another line: see `design_line`)
 
 A "step" is one decode step. The default run has the layer sizes of the 2B configuration
 (26 layers, hidden 2304, 8 heads over 4 kv heads of 256, intermediate 9216, vocabulary 256000,
@@ -362,6 +363,165 @@ class Bench:
         self.torch.cuda.empty_cache()
 
 
+# ---------------------------------------------------------------------------------------------
+# --design fusitar: the Fusitar design (attention with kept first keys and a gate, mLSTM, mixture
+# of experts) beside Gemma 2 at equal sizes: the same width, heads, head size, window, vocabulary,
+# as many layers, and as much feed-forward a token (top x expert size = Gemma's intermediate size).
+DESIGN_SIZES = {
+    # name: width, heads, kv heads, head size, window, first keys kept, experts, top, groups, kept groups, expert size, vocab, layers
+    "s": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, keep=4, experts=16, top=4, groups=4, keep_groups=2, ff=1024, vocab=32768, layers=4),
+    "m": dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, keep=4, experts=32, top=4, groups=8, keep_groups=4, ff=2048, vocab=32768, layers=4),
+}
+DESIGN_HISTORY = 3072
+DESIGN_BATCH = 8
+
+
+def fusitar_config(z):
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"], "keep": z["keep_groups"]}}}
+    att = {"type": "attention", "mlp": moe, "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                                                        "scale": z["dim"] ** -0.5, "mask": {"size": z["window"], "keep_first": z["keep"]}}}
+    rec = {"type": "mlstm", "mlp": moe, "mixer": {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "gate_cap": 15.0}}
+    return {"architecture": "Fusitar", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": z["width"] ** 0.5},
+            "norm": {"eps": 1e-6}, "layers": [att if i % 2 == 0 else rec for i in range(z["layers"])]}
+
+
+def gemma_config(z):
+    return {"architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2", "num_hidden_layers": z["layers"], "hidden_size": z["width"],
+            "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"], "head_dim": z["dim"],
+            "intermediate_size": z["top"] * z["ff"], "vocab_size": z["vocab"], "sliding_window": z["window"],
+            "layer_types": ["sliding_attention"] * z["layers"], "query_pre_attn_scalar": z["dim"], "attn_logit_softcapping": 50.0,
+            "final_logit_softcapping": 30.0, "rms_norm_eps": 1e-6, "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True}
+
+
+def design_kernel_rooflines(which, z, kind, rows, context, batch, pk):
+    """{kernel entry point: (what it must do, in flops or bytes)} for one pass: `kind` "prefill" (rows
+    tokens of one request from position 0) or "decode" (batch requests of `context` positions)."""
+    w, hq, hkv, d, win = z["width"], z["heads"], z["kv_heads"], z["dim"], z["window"]
+    layers = z["layers"]
+    att_layers = layers if which == "gemma2" else (layers + 1) // 2
+    rec_layers = 0 if which == "gemma2" else layers // 2
+    out = {}
+    if kind == "prefill":
+        pairs = sum(min(c, win) for c in range(1, rows + 1))
+        out["attention"] = ("flops", att_layers * 4.0 * pairs * hq * d)
+        out["feed_forward"] = ("flops", layers * 2.0 * rows * 3 * z["top"] * z["ff"] * w if which == "gemma2" else layers * 2.0 * rows * 2 * z["top"] * z["ff"] * w)
+        out["mlstm_scan"] = ("flops", rec_layers * 4.0 * rows * hq * d * d)
+    else:
+        out["attention"] = ("bytes", att_layers * batch * min(context, win) * hkv * d * 2 * 2.0)
+        experts_read = min(z["experts"], batch * z["top"])
+        out["feed_forward"] = ("bytes", layers * 3.0 * z["top"] * z["ff"] * w * 2 if which == "gemma2" else layers * experts_read * 2.0 * z["ff"] * w * 2)
+        out["mlstm_scan"] = ("bytes", rec_layers * batch * hq * d * d * 4 * 2.0)
+    return out
+
+
+# Which timed entry points make up a like kernel of the two designs.
+KERNEL_CLASSES = {
+    "attention": ("paged_attention_rows", "paged_attention_mma", "paged_attention_decode_fused"),
+    "feed_forward": ("moe_grouped", "gemm_glu_fused", "glu", "gemm:ffn"),
+    "mlstm_scan": ("mlstm_scan",),
+}
+
+
+def design_point(which, z, steps, warmup, clocks, pk):
+    """Prefill of 2,048 tokens and decode at batch 8 for one design at one size: tokens a second through
+    the engine (recorded passes), and the device time of each kernel entry point in one eager pass."""
+    import numpy as np
+    import torch
+
+    from kapel_b200 import kernels as K
+    from kapel_b200.engine import Engine, StepEntry
+
+    cfg = fusitar_config(z) if which == "fusitar" else gemma_config(z)
+    room = (DESIGN_BATCH + 1) * (DESIGN_HISTORY + 4 * (steps + warmup) + 128) + PREFILL_TOKENS
+    engine = Engine.random(cfg, seed=0, dtype="bfloat16", max_tokens=room, max_sequences=DESIGN_BATCH + 2)
+    rng = np.random.default_rng(0)
+    tokens = lambda n: [int(t) for t in rng.integers(0, z["vocab"], size=n)]
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        clocks.active = True
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        clocks.active = False
+        return a.elapsed_time(b) / n
+
+    def prefill_once():
+        engine.step([StepEntry("p", tokens(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+        engine.end("p")
+
+    for _ in range(3):
+        prefill_once()
+    prefill_ms = min(timed(prefill_once, 1) for _ in range(3))
+    ids = [f"s{i}" for i in range(DESIGN_BATCH)]
+    for sid in ids:
+        for at in range(0, DESIGN_HISTORY, PREFILL_TOKENS):
+            engine.step([StepEntry(sid, tokens(min(PREFILL_TOKENS, DESIGN_HISTORY - at)), [])])
+    decode_once = lambda: engine.step([StepEntry(sid, tokens(1), [0]) for sid in ids])
+    for _ in range(warmup):
+        decode_once()
+    decode_ms = timed(decode_once, steps)
+    # one eager pass of each kind with every entry point between two events
+    engine.graphs = engine.prompt_graphs = None
+    K.enable_timing()
+    per_kernel = {}
+    for kind, fn in (("prefill", prefill_once), ("decode", decode_once)):
+        fn()
+        K.timing_report()
+        fn()
+        rows = K.timing_report()
+        must = design_kernel_rooflines(which, z, kind, PREFILL_TOKENS, DESIGN_HISTORY, DESIGN_BATCH, pk)
+        classes = {}
+        for name, shape, calls, ms in rows:
+            for cls, members in KERNEL_CLASSES.items():
+                if name in members:
+                    classes[cls] = classes.get(cls, 0.0) + ms
+        if which == "gemma2":          # Gemma's way down is a plain product: count the products whose inner width is the intermediate size
+            classes["feed_forward"] = classes.get("feed_forward", 0.0) + sum(
+                ms for name, shape, calls, ms in rows if name == "gemm" and len(shape) == 2 and shape[0] == z["width"] and shape[1] == z["top"] * z["ff"])
+        rec = {"kernels": [{"name": n, "shape": list(sh), "calls": c, "ms": round(ms, 4)} for n, sh, c, ms in rows][:14], "classes": {}}
+        for cls, ms in classes.items():
+            unit, amount = must[cls]
+            if amount <= 0 or ms <= 0:
+                continue
+            peak = pk["bf16_tflops"] * 1e12 if unit == "flops" else pk["hbm_gbs"] * 1e9
+            rec["classes"][cls] = {"ms": round(ms, 4), "bound": unit, "frac_of_measured_peak": amount / (ms * 1e-3) / peak}
+        per_kernel[kind] = rec
+    K.disable_timing()
+    K.check_async_errors()
+    out = {"prefill_tok_s": PREFILL_TOKENS / prefill_ms * 1e3, "prefill_ms": prefill_ms, "decode_tok_s": DESIGN_BATCH / decode_ms * 1e3,
+           "decode_ms": decode_ms, "batch": DESIGN_BATCH, "history": DESIGN_HISTORY, "by_kernel": per_kernel}
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def design_line(args) -> int:
+    import torch
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    clocks = ClockSampler()
+    sizes = {}
+    for name in args.design_sizes.split(","):
+        z = DESIGN_SIZES[name]
+        sizes[name] = {"shape": z, "fusitar": design_point("fusitar", z, min(args.steps, 50), max(3, args.warmup), clocks, pk),
+                       "gemma2": design_point("gemma2", z, min(args.steps, 50), max(3, args.warmup), clocks, pk)}
+    clocks.close()
+    first = sizes[args.design_sizes.split(",")[0]]
+    print(json.dumps({
+        "metric": f"decode tok/s at batch {DESIGN_BATCH} (Fusitar, size {args.design_sizes.split(',')[0]}, bf16, {DESIGN_HISTORY} tokens of history per sequence)",
+        "value": first["fusitar"]["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+        "data": "synthetic: seeded random weights and uniform-random token ids", "design": "fusitar", "beside": "gemma2 at equal sizes",
+        "config": {"peaks": pk["source"], "prefill_tokens": PREFILL_TOKENS}, "sizes": sizes, "clocks": clocks.summary(), "impl": "ours"}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -378,6 +538,9 @@ def main() -> int:
     ap.add_argument("--skip-check", action="store_true", help="leave out the check of the timed logits against the 32-bit path")
     ap.add_argument("--breakdown", action="store_true",
                     help="instead of the JSON line: device time by kernel for one prefill step and one eager decode step")
+    ap.add_argument("--design", default=None, choices=["fusitar"],
+                    help="instead of the default line: this design beside Gemma 2 at equal sizes, prefill and decode, with each like kernel's roofline fraction")
+    ap.add_argument("--design-sizes", default="s,m", help="which of the design sizes (s, m), comma separated")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -386,6 +549,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.design is not None:
+        return design_line(args)
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
 

@@ -15,9 +15,7 @@ extern "C" int kb_paged_attention_rows(void* out, const void* q, const void* k_t
                                        int hq, int hkv, int d, int dv, int page_size, int table_width, int n_pages, int window,
                                        int keep, int slots, float scale, float cap, float* scratch, void* stream) {
     KB_REQUIRE(rows >= 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "paged_attention: rows %d, heads %d over %d kv heads", rows, hq, hkv);
-    const int vec = dt == KB_DT_F32 ? 4 : 8;
-    KB_REQUIRE(d > 0 && d % vec == 0, "paged_attention: head_dim %d must be a multiple of %d (16-byte pieces of a key)", d, vec);
-    KB_REQUIRE(dv > 0 && dv % 2 == 0, "paged_attention: the values' size %d must be even", dv);
+    KB_REQUIRE(d > 0 && dv > 0, "paged_attention: head sizes %d / %d", d, dv);
     KB_REQUIRE(keep >= 0, "paged_attention: %d first keys kept", keep);
     KB_REQUIRE(page_size > 0 && table_width > 0 && n_pages > 0, "paged_attention: page_size %d, table width %d, pages %d", page_size, table_width, n_pages);
     KB_REQUIRE(window >= 0 && slots >= 1 && slots <= 65535, "paged_attention: window %d, chunk slots %d", window, slots);
@@ -29,7 +27,7 @@ extern "C" int kb_paged_attention_rows(void* out, const void* q, const void* k_t
     p.q = q; p.k_table = k_table; p.v_table = v_table; p.block_table = block_table; p.row_entry = row_entry;
     p.row_count = row_count; p.out = out; p.partial = slots > 1 ? scratch : nullptr;
     p.rows = rows; p.hq = hq; p.hkv = hkv; p.d = d; p.page_size = page_size; p.table_width = table_width;
-    p.n_pages = n_pages; p.dv = dv; p.window = window; p.keep = window > 0 ? keep : 0;
+    p.n_pages = n_pages; p.dv = dv; p.vec = (d % (dt == KB_DT_F32 ? 4 : 8)) == 0 && ((uintptr_t)k_table & 15) == 0; p.window = window; p.keep = window > 0 ? keep : 0;
     p.keep_slots = p.keep > 0 ? (p.keep + ATT_CHUNK - 1) / ATT_CHUNK : 0;
     KB_REQUIRE(slots > p.keep_slots, "paged_attention: %d slots of which %d are the kept first keys'", slots, p.keep_slots);
     p.slots = slots; p.scale = scale; p.cap = cap;

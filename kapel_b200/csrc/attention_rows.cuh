@@ -60,6 +60,7 @@ struct AttParams {
     float* partial;           // [rows, hq, slots, dv + 2] or null when slots == 1
     int rows, hq, hkv, d, page_size, table_width, n_pages;
     int dv;                   // the values' size (the v table is [pages, hkv, page_size, dv])
+    int vec;                  // 1: a key is a whole number of 16-byte pieces and is loaded as such
     int window;               // 0: none
     int keep;                 // with a window: the keys [0, keep) stay visible below it
     int keep_slots;           // ceil(keep / CHUNK) with a window and keep > 0, else 0: the slots of those keys
@@ -113,16 +114,22 @@ rows_kernel(const AttParams p) {
         return;
     }
 
-    // shared: q [GMAX][d] | scores [GMAX][CHUNK] | lines [CHUNK] | stats [2*GMAX] | acc [groups][GMAX][d]
+    // shared: q [GMAX][dq] | scores [GMAX][CHUNK] | lines [CHUNK] | stats [2*GMAX] | acc [groups][GMAX][dv]
+    // (dq: d rounded up to whole 16-byte pieces, the rest zeros)
+    const int nvec = (d + VN - 1) / VN;
+    const int dq = nvec * VN;
     float* sq = smem;
-    float* ss = sq + GMAX * d;
+    float* ss = sq + GMAX * dq;
     int* sline = reinterpret_cast<int*>(ss + GMAX * ATT_CHUNK);
     float* sstat = reinterpret_cast<float*>(sline + ATT_CHUNK);
     float* sacc = sstat + 2 * GMAX;
 
     const int entry = p.row_entry[r];
     const T* q = static_cast<const T*>(p.q) + ((size_t)r * p.hq + kvh * group + g0) * d;
-    for (int i = tid; i < gn * d; i += ATT_THREADS) sq[i] = Elem<T>::load(q + i);
+    for (int i = tid; i < gn * dq; i += ATT_THREADS) {
+        const int g = i / dq, c = i - g * dq;
+        sq[i] = c < d ? Elem<T>::load(q + (size_t)g * d + c) : 0.f;
+    }
     for (int j = tid; j < nkeys; j += ATT_THREADS) {
         const int pos = lo + j;
         const int lp = pos / p.page_size;
@@ -137,7 +144,6 @@ rows_kernel(const AttParams p) {
     const T* kt = static_cast<const T*>(p.k_table);
     constexpr int KPW = 32 / LPK;                          // keys a warp handles at a time
     const int sub = lane / LPK, li = lane % LPK;
-    const int nvec = d / VN;
     for (int j0 = warp * KPW; j0 < nkeys; j0 += ATT_WARPS * KPW) {
         const int j = j0 + sub;
         const bool live = j < nkeys;
@@ -146,8 +152,12 @@ rows_kernel(const AttParams p) {
 #pragma unroll
         for (int v = 0; v < VPL; ++v) {
             const int vi = li + v * LPK;
-            if (line >= 0 && vi < nvec) {
+            if (line >= 0 && vi < nvec && p.vec) {
                 Vec<T>::load(kt + kv_row(line, kvh, p.hkv, p.page_size) * d + vi * VN, kv[v]);
+            } else if (line >= 0 && vi < nvec) {
+                const T* kp = kt + kv_row(line, kvh, p.hkv, p.page_size) * d;
+#pragma unroll
+                for (int e = 0; e < VN; ++e) kv[v][e] = vi * VN + e < d ? Elem<T>::load(kp + vi * VN + e) : 0.f;
             } else {
 #pragma unroll
                 for (int e = 0; e < VN; ++e) kv[v][e] = 0.f;
@@ -160,7 +170,7 @@ rows_kernel(const AttParams p) {
                 const int vi = li + v * LPK;
                 if (vi < nvec) {
 #pragma unroll
-                    for (int e = 0; e < VN; ++e) dot = fmaf(kv[v][e], sq[g * d + vi * VN + e], dot);
+                    for (int e = 0; e < VN; ++e) dot = fmaf(kv[v][e], sq[g * dq + vi * VN + e], dot);
                 }
             }
 #pragma unroll
@@ -194,7 +204,8 @@ rows_kernel(const AttParams p) {
     // ---- weighted sum of values: a thread owns two neighbouring components; thread groups of
     // d/2 share the keys when d/2 < ATT_THREADS, and add up in group order afterwards.
     const T* vt = static_cast<const T*>(p.v_table);
-    const int pairs = dv / 2;
+    const int pairs = (dv + 1) / 2;
+    const int dvs = 2 * pairs;                              // a row of the groups' partial sums
     const int tgroups = pairs >= ATT_THREADS ? 1 : ATT_THREADS / pairs;
     const int tg = tid / pairs;                            // this thread's group (may be >= tgroups)
     float acc[GMAX][2];
@@ -207,7 +218,7 @@ rows_kernel(const AttParams p) {
                 const int line = sline[j];
                 if (line < 0) continue;
                 const T* vp = vt + kv_row(line, kvh, p.hkv, p.page_size) * dv + 2 * pi;
-                const float v0 = Elem<T>::load(vp), v1 = Elem<T>::load(vp + 1);
+                const float v0 = Elem<T>::load(vp), v1 = 2 * pi + 1 < dv ? Elem<T>::load(vp + 1) : 0.f;
 #pragma unroll
                 for (int g = 0; g < GMAX; ++g) {
                     if (g < gn) {
@@ -223,8 +234,8 @@ rows_kernel(const AttParams p) {
 #pragma unroll
                 for (int g = 0; g < GMAX; ++g)
                     if (g < gn) {
-                        sacc[((size_t)tg * GMAX + g) * dv + 2 * pi] = acc[g][0];
-                        sacc[((size_t)tg * GMAX + g) * dv + 2 * pi + 1] = acc[g][1];
+                        sacc[((size_t)tg * GMAX + g) * dvs + 2 * pi] = acc[g][0];
+                        sacc[((size_t)tg * GMAX + g) * dvs + 2 * pi + 1] = acc[g][1];
                     }
             }
             __syncthreads();
@@ -233,8 +244,8 @@ rows_kernel(const AttParams p) {
                 for (int g = 0; g < GMAX; ++g)
                     if (g < gn)
                         for (int x = 1; x < tgroups; ++x) {
-                            acc[g][0] += sacc[((size_t)x * GMAX + g) * dv + 2 * pi];
-                            acc[g][1] += sacc[((size_t)x * GMAX + g) * dv + 2 * pi + 1];
+                            acc[g][0] += sacc[((size_t)x * GMAX + g) * dvs + 2 * pi];
+                            acc[g][1] += sacc[((size_t)x * GMAX + g) * dvs + 2 * pi + 1];
                         }
             }
         }
@@ -248,11 +259,11 @@ rows_kernel(const AttParams p) {
                     const float inv = l > 0.f ? 1.f / l : 0.f;
                     T* o = out + ((size_t)r * p.hq + h) * dv + 2 * pi;
                     Elem<T>::store(o, acc[g][0] * inv);
-                    Elem<T>::store(o + 1, acc[g][1] * inv);
+                    if (2 * pi + 1 < dv) Elem<T>::store(o + 1, acc[g][1] * inv);
                 } else {
                     float* o = p.partial + (((size_t)r * p.hq + h) * p.slots + blockIdx.z) * (dv + 2);
                     o[2 * pi] = acc[g][0];
-                    o[2 * pi + 1] = acc[g][1];
+                    if (2 * pi + 1 < dv) o[2 * pi + 1] = acc[g][1];
                     if (pi == 0) { o[dv] = sstat[2 * g]; o[dv + 1] = sstat[2 * g + 1]; }
                 }
             }
@@ -299,10 +310,11 @@ __global__ void combine_kernel(const AttParams p) {
 }
 
 static size_t rows_smem_bytes(int gmax, int d, int dv) {
-    const int pairs = dv / 2;
+    const int pairs = (dv + 1) / 2;
     const int tgroups = pairs >= ATT_THREADS ? 1 : ATT_THREADS / pairs;
-    size_t floats = (size_t)gmax * d + (size_t)gmax * ATT_CHUNK + ATT_CHUNK + 2 * gmax;
-    if (tgroups > 1) floats += (size_t)tgroups * gmax * dv;
+    const int dq = (d + 7) / 8 * 8;                          // room for d rounded up to either element type's pieces
+    size_t floats = (size_t)gmax * dq + (size_t)gmax * ATT_CHUNK + ATT_CHUNK + 2 * gmax;
+    if (tgroups > 1) floats += (size_t)tgroups * gmax * (dv + 1);
     return floats * sizeof(float);
 }
 
@@ -321,7 +333,7 @@ static int launch_rows(const AttParams& p, cudaStream_t s) {
 
 template <typename T, int GMAX>
 static int dispatch_lanes(const AttParams& p, cudaStream_t s) {
-    const int nvec = p.d / Vec<T>::N;                     // 16-byte vectors of a key
+    const int nvec = (p.d + Vec<T>::N - 1) / Vec<T>::N;   // 16-byte pieces of a key, the last maybe in part
     int lpk = 1;
     while (lpk * 2 <= nvec && lpk < 32) lpk *= 2;
     const int vpl = (nvec + lpk - 1) / lpk;

@@ -1,10 +1,12 @@
 """Builds the CUDA library of this package for sm_100a with nvcc, once, and finds it again; and the
 small host library (`host/*.cpp`: the cache manager's bookkeeping) with the C++ compiler alone.
 
-`ensure_built()` returns the path of `libkapel_b200.so`. It compiles every `.cu` file of this
+`ensure_built()` returns the path of `libkapel_b200.so`. It compiles the `.cu` files of this
 folder in parallel when the library is missing or older than its sources (a stamp beside it
 holds a hash of sources and flags), printing a line as each file finishes and one every few
-seconds meanwhile, so a first call in a fresh checkout shows that it is alive. The library
+seconds meanwhile, so a first call in a fresh checkout shows that it is alive. Every object has
+a stamp of its own (its source, the headers, the flags): a file that has not changed since its
+object was made is not compiled again. The library
 lands in `_build/` beside the sources; if that folder cannot be written, in a per-user folder
 under the system's temporary directory (or `$KAPEL_B200_BUILD_DIR`).
 
@@ -57,6 +59,16 @@ def _nvcc() -> str:
 def _stamp() -> str:
     h = hashlib.sha256()
     for f in sources() + _headers():
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _object_stamp(src: Path) -> str:
+    h = hashlib.sha256()
+    h.update(src.read_bytes())
+    for f in _headers():
         h.update(f.name.encode())
         h.update(f.read_bytes())
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
@@ -121,9 +133,17 @@ def ensure_built(verbose: bool = True, force: bool = False) -> Path:
     threading.Thread(target=ticker, daemon=True).start()
 
     def compile_one(src: Path):
-        obj = out / (src.stem + ".o")
+        obj, mark = out / (src.stem + ".o"), out / (src.stem + ".o.stamp")
+        want = _object_stamp(src)
+        try:
+            if not force and obj.is_file() and mark.is_file() and mark.read_text().strip() == want:
+                return src, obj, None                          # unchanged since its object was made
+        except OSError:
+            pass
         cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", str(HERE), "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode == 0:
+            mark.write_text(want)
         return src, obj, r
 
     try:
@@ -132,10 +152,10 @@ def ensure_built(verbose: bool = True, force: bool = False) -> Path:
             futures = [pool.submit(compile_one, s) for s in srcs]
             for fut in as_completed(futures):
                 src, obj, r = fut.result()
-                if r.returncode != 0:
+                if r is not None and r.returncode != 0:
                     raise RuntimeError(f"kapel_b200: nvcc failed on {src.name}:\n{r.stdout}\n{r.stderr}")
                 objs.append(obj)
-                _say(f"compiled {src.name} ({time.time() - t0:.0f} s)", verbose)
+                _say(f"compiled {src.name} ({time.time() - t0:.0f} s)" if r is not None else f"kept {obj.name}", verbose)
         tmp = out / (LIB_NAME + f".tmp{os.getpid()}")
         cmd = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp), *[str(o) for o in sorted(objs)]]
         r = subprocess.run(cmd, capture_output=True, text=True)

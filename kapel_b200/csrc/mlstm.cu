@@ -12,7 +12,11 @@
 // the memory's rows j = jg, jg + MJ, ... of one value component c, and the normaliser's same rows
 // (every slice keeps a copy of n and m of its own, so slices never read what another writes).
 // The MJ threads of a component are neighbouring lanes and add up by shuffles. The rows of a
-// request are walked in order; the next row's inputs are loaded while this row's are used.
+// request are walked in order. Their inputs (k, q, the slice's v, the two gates) come into shared
+// memory a chunk of rows at a time, every value fetched (and, for split-K partial sums, added up)
+// once a block; from a float32 tensor the next chunk arrives by asynchronous copies while this one
+// is walked. A slice's part of the memory lies in the state table in the order of the threads
+// that hold it, so it is read and written in whole lines.
 #include "common.cuh"
 
 namespace kb {
@@ -41,18 +45,29 @@ struct MlstmParams {
     float cap, q_scale, floor_;
 };
 
-// Floats of one head's state: S [d][e], then a copy of n [d] and of m for every slice.
+// Floats of one slice of one head's state: the memory's rows in the threads' order
+// [ceil(d / MJ)][MV * MJ], then the slice's copy of n [d] and of m.
+__host__ __device__ inline long long mlstm_slice_floats(int d) {
+    return (long long)((d + MJ - 1) / MJ) * MLSTM_THREADS + d + 1;
+}
 __host__ __device__ inline long long mlstm_state_floats(int d, int e) {
-    const int slices = (e + MV - 1) / MV;
-    return (long long)d * e + (long long)slices * (d + 1);
+    return (long long)((e + MV - 1) / MV) * mlstm_slice_floats(d);
 }
 
-template <typename TS, int R>
+__device__ __forceinline__ void mlstm_copy4(float* dst, const float* src) {
+    const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d32), "l"(src) : "memory");
+}
+
+// R: memory rows a thread holds (d <= R * MJ); CH: rows of the step staged at a time.
+template <typename TS, int R, int CH>
 __global__ void __launch_bounds__(MLSTM_THREADS)
 mlstm_scan_kernel(const Src<TS> src, const MlstmParams p) {
+    extern __shared__ float staged[];                        // [2][CH][rowf]
     const int entry = blockIdx.x, head = blockIdx.y, slice = blockIdx.z;
-    const int c = slice * MV + (threadIdx.x / MJ);
-    const int jg = threadIdx.x % MJ;
+    const int tid = threadIdx.x;
+    const int cl = tid / MJ, c = slice * MV + cl;
+    const int jg = tid % MJ;
     const bool live = c < p.e;
     const int r0 = p.entry_start[entry], r1 = p.entry_end[entry];
     if (r1 <= r0) return;
@@ -63,76 +78,109 @@ mlstm_scan_kernel(const Src<TS> src, const MlstmParams p) {
             for (int r = r0; r < r1; ++r) p.out[((size_t)r * p.heads + head) * e + c] = 0.f;
         return;
     }
-    float* st = p.state + ((size_t)slot * p.heads + head) * mlstm_state_floats(d, e);
-    float* st_n = st + (size_t)d * e + (size_t)slice * (d + 1);
+    float* st = p.state + ((size_t)slot * p.heads + head) * mlstm_state_floats(d, e) + (size_t)slice * mlstm_slice_floats(d);
+    float* st_n = st + (size_t)((d + MJ - 1) / MJ) * MLSTM_THREADS;
     float S[R], n[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int j = jg + i * MJ;
-        S[i] = (live && j < d) ? st[(size_t)j * e + c] : 0.f;
+        S[i] = j < d ? st[(size_t)i * MLSTM_THREADS + tid] : 0.f;
         n[i] = j < d ? st_n[j] : 0.f;
     }
     float m = st_n[d];
     const float bi = p.bias_i[head], bf = p.bias_f[head];
 
-    // Two sets of inputs, taken in turn (named apart, so that both stay in registers).
-    float k0[R], q0[R], k1[R], q1[R], v0, v1, zi0, zi1, zf0, zf1;
-    auto fetch = [&](int r, float (&kk)[R], float (&qq)[R], float& vv, float& zi, float& zf) {
-        const size_t base = (size_t)r * p.row_width;
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const int j = jg + i * MJ;
-            kk[i] = j < d ? src.at(base + p.k_off + (size_t)head * d + j) : 0.f;
-            qq[i] = j < d ? src.at(base + p.q_off + (size_t)head * d + j) : 0.f;
+    const int rowf = 2 * d + MV + 2;                         // k [d] | q [d] | v [MV] | zi | zf
+    bool async = false;
+    if constexpr (sizeof(TS) == 4) async = src.splits == 1;
+    auto stage = [&](int chunk, int buf) {
+        const int rbase = r0 + chunk * CH;
+        const int nr = min(CH, r1 - rbase);
+        for (int idx = tid; idx < nr * rowf; idx += MLSTM_THREADS) {
+            const int t = idx / rowf, x = idx - t * rowf;
+            size_t col;
+            bool ok = true;
+            if (x < d) col = (size_t)p.k_off + (size_t)head * d + x;
+            else if (x < 2 * d) col = (size_t)p.q_off + (size_t)head * d + (x - d);
+            else if (x < 2 * d + MV) {
+                const int cc = slice * MV + (x - 2 * d);
+                ok = cc < e;
+                col = (size_t)p.v_off + (size_t)head * e + (ok ? cc : 0);
+            } else col = (size_t)(x == 2 * d + MV ? p.i_off : p.f_off) + head;
+            float* dst = staged + ((size_t)buf * CH + t) * rowf + x;
+            const size_t at = (size_t)(rbase + t) * p.row_width + col;
+            if (!ok) *dst = 0.f;
+            else if (async) mlstm_copy4(dst, reinterpret_cast<const float*>(src.p) + at);
+            else *dst = src.at(at);
         }
-        vv = live ? src.at(base + p.v_off + (size_t)head * e + c) : 0.f;
-        zi = src.at(base + p.i_off + head);
-        zf = src.at(base + p.f_off + head);
+        if (async) asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    auto step = [&](int r, const float (&kk)[R], const float (&qq)[R], float vv, float zi, float zf) {
-        const float gi = p.cap * tanhf((zi + bi) / p.cap);
-        const float gf = log_sigmoid(p.cap * tanhf((zf + bf) / p.cap));
-        const float m_new = fmaxf(gf + m, gi);
-        const float fa = expf(gf + m - m_new);
-        const float fb = expf(gi - m_new);
-        m = m_new;
-        const float bv = fb * vv;
-        float acc = 0.f, nq = 0.f;
+    const int chunks = (r1 - r0 + CH - 1) / CH;
+    stage(0, 0);
+    for (int ch = 0; ch < chunks; ++ch) {
+        if (async) {
+            if (ch + 1 < chunks) {
+                stage(ch + 1, (ch + 1) & 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+        }
+        __syncthreads();
+        const int rbase = r0 + ch * CH;
+        const int nr = min(CH, r1 - rbase);
+        float* rows = staged + (size_t)(ch & 1) * CH * rowf;
+        // The chunk's gates, each once, ahead of the walk: they depend on no state.
+        if (tid < nr) {
+            float* in = rows + (size_t)tid * rowf;
+            const float gi = p.cap * tanhf((in[2 * d + MV] + bi) / p.cap);
+            const float gf = log_sigmoid(p.cap * tanhf((in[2 * d + MV + 1] + bf) / p.cap));
+            in[2 * d + MV] = gi;
+            in[2 * d + MV + 1] = gf;
+        }
+        __syncthreads();
+        for (int t = 0; t < nr; ++t) {
+            const float* in = rows + (size_t)t * rowf;
+            const float gi = in[2 * d + MV], gf = in[2 * d + MV + 1];
+            const float m_new = fmaxf(gf + m, gi);
+            const float fa = expf(gf + m - m_new);
+            const float fb = expf(gi - m_new);
+            m = m_new;
+            const float bv = fb * in[2 * d + cl];
+            float acc[2] = {0.f, 0.f}, nq[2] = {0.f, 0.f};     // two chains each, rows in turn
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const float q = qq[i] * p.q_scale;
-            S[i] = fmaf(fa, S[i], kk[i] * bv);
-            n[i] = fmaf(fa, n[i], fb * kk[i]);
-            acc = fmaf(S[i], q, acc);
-            nq = fmaf(n[i], q, nq);
-        }
+            for (int i = 0; i < R; ++i) {
+                const int j = jg + i * MJ;
+                const float kk = j < d ? in[j] : 0.f;
+                const float q = j < d ? in[d + j] * p.q_scale : 0.f;
+                S[i] = fmaf(fa, S[i], kk * bv);
+                n[i] = fmaf(fa, n[i], fb * kk);
+                acc[i & 1] = fmaf(S[i], q, acc[i & 1]);
+                nq[i & 1] = fmaf(n[i], q, nq[i & 1]);
+            }
+            float a = acc[0] + acc[1], b = nq[0] + nq[1];
 #pragma unroll
-        for (int o = MJ / 2; o > 0; o >>= 1) {
-            acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            nq += __shfl_xor_sync(0xffffffffu, nq, o);
+            for (int o = MJ / 2; o > 0; o >>= 1) {
+                a += __shfl_xor_sync(0xffffffffu, a, o);
+                b += __shfl_xor_sync(0xffffffffu, b, o);
+            }
+            if (live && jg == 0) {
+                const float denom = fmaxf(fabsf(b), expf(-m)) + p.floor_;
+                p.out[((size_t)(rbase + t) * p.heads + head) * e + c] = a / denom;
+            }
         }
-        if (live && jg == 0) {
-            const float denom = fmaxf(fabsf(nq), expf(-m)) + p.floor_;
-            p.out[((size_t)r * p.heads + head) * e + c] = acc / denom;
-        }
-    };
-    fetch(r0, k0, q0, v0, zi0, zf0);
-    for (int r = r0; r < r1; r += 2) {
-        if (r + 1 < r1) fetch(r + 1, k1, q1, v1, zi1, zf1);
-        step(r, k0, q0, v0, zi0, zf0);
-        if (r + 1 >= r1) break;
-        if (r + 2 < r1) fetch(r + 2, k0, q0, v0, zi0, zf0);
-        step(r + 1, k1, q1, v1, zi1, zf1);
+        __syncthreads();                                     // the chunk's buffer may be written again
+        if (!async && ch + 1 < chunks) stage(ch + 1, (ch + 1) & 1);
     }
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int j = jg + i * MJ;
         if (j < d) {
-            if (live) st[(size_t)j * e + c] = S[i];
-            if (threadIdx.x / MJ == 0) st_n[j] = n[i];       // the slice's first component writes its copy of n
+            st[(size_t)i * MLSTM_THREADS + tid] = live ? S[i] : 0.f;
+            if (cl == 0) st_n[j] = n[i];                     // the slice's first component writes its copy of n
         }
     }
-    if (threadIdx.x == 0) st_n[d] = m;
+    if (tid == 0) st_n[d] = m;
 }
 
 }  // namespace kb
@@ -165,13 +213,15 @@ extern "C" int kb_mlstm_scan(float* out, const void* src, int in_dt, int splits,
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(entries, heads, slices);
     const int need = (d + MJ - 1) / MJ;
-#define KB_MLSTM(TS, R) mlstm_scan_kernel<TS, R><<<grid, MLSTM_THREADS, 0, s>>>(Src<TS>{(const TS*)src, splits, (size_t)split_stride}, p)
-#define KB_MLSTM_R(TS)                       \
-    do {                                     \
-        if (need <= 4) KB_MLSTM(TS, 4);      \
-        else if (need <= 8) KB_MLSTM(TS, 8); \
-        else if (need <= 16) KB_MLSTM(TS, 16); \
-        else KB_MLSTM(TS, 32);               \
+#define KB_MLSTM(TS, R, CH)                                                                                        \
+    mlstm_scan_kernel<TS, R, CH><<<grid, MLSTM_THREADS, (size_t)2 * CH * (2 * d + MV + 2) * sizeof(float), s>>>( \
+        Src<TS>{(const TS*)src, splits, (size_t)split_stride}, p)
+#define KB_MLSTM_R(TS)                             \
+    do {                                           \
+        if (need <= 4) KB_MLSTM(TS, 4, 16);        \
+        else if (need <= 8) KB_MLSTM(TS, 8, 16);   \
+        else if (need <= 16) KB_MLSTM(TS, 16, 16); \
+        else KB_MLSTM(TS, 32, 8);                  \
     } while (0)
     if (in_dt == KB_DT_F32) KB_MLSTM_R(float);
     else if (in_dt == KB_DT_BF16) KB_MLSTM_R(bf16);

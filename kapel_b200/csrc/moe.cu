@@ -162,7 +162,6 @@ constexpr int GN = 64;         // columns of a tile
 constexpr int GK = 32;         // k step
 constexpr int GEMM_THREADS = 128;
 
-template <typename T> struct Acts;
 __device__ __forceinline__ float moe_act(float v, int act) {
     if (act == 1) { const float r = fmaxf(v, 0.f); return r * r; }     // the square of relu
     if (act == 2) return gelu_tanh(v);
@@ -239,13 +238,25 @@ moe_grouped_f32_kernel(const GroupedParams p) {
 }
 
 // bfloat16 operands, 32-bit sums by mma.sync m16n8k16; four warps, each all 32 rows x 16 columns.
+// Tiles of BK k values arrive by 16-byte asynchronous copies, three stages deep, so that a block
+// that walks one expert's weights for a handful of rows (a decoding step) keeps loads in flight
+// instead of waiting for each tile; rows of k that are no multiple of 8 are loaded value by value.
+constexpr int BK = 64;
+constexpr int BSTAGES = 3;
+
+__device__ __forceinline__ void moe_copy16(void* dst, const void* src, bool valid) {
+    const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;                        // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d32), "l"(src), "r"(bytes) : "memory");
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(GEMM_THREADS)
 moe_grouped_bf16_kernel(const GroupedParams p) {
     const int tile = blockIdx.x;
     if (tile >= p.n_tiles[0]) return;
-    __shared__ __align__(16) bf16 As[GM][GK + 8];
-    __shared__ __align__(16) bf16 Ws[GN][GK + 8];
+    __shared__ __align__(16) bf16 As[BSTAGES][GM][BK + 8];
+    __shared__ __align__(16) bf16 Ws[BSTAGES][GN][BK + 8];
     __shared__ int arow[GM], orow[GM];
     const int expert = p.tile_expert[tile], first = p.tile_first[tile], nrows = p.tile_rows[tile];
     const int n0 = blockIdx.y * GN;
@@ -260,49 +271,60 @@ moe_grouped_bf16_kernel(const GroupedParams p) {
     const bf16* A = static_cast<const bf16*>(p.a);
     const bf16* W = static_cast<const bf16*>(p.w) + (size_t)expert * p.n * p.k;
     const bool vec = (p.k % 8) == 0 && ((((uintptr_t)A) | ((uintptr_t)W)) & 15) == 0;
-    float acc[2][2][4] = {};
-    const int grp = lane >> 2, qd = lane & 3;
-    for (int k0 = 0; k0 < p.k; k0 += GK) {
+    const int nk = (p.k + BK - 1) / BK;
+    auto load_stage = [&](int kt, int st) {
+        const int k0 = kt * BK;
         if (vec) {
-            for (int i = tid; i < GM * (GK / 8); i += GEMM_THREADS) {
-                const int row = i / (GK / 8), kk = (i % (GK / 8)) * 8;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (k0 + kk < p.k) v = *reinterpret_cast<const uint4*>(A + (size_t)arow[row] * p.k + k0 + kk);
-                *reinterpret_cast<uint4*>(&As[row][kk]) = v;
+            for (int i = tid; i < GM * (BK / 8); i += GEMM_THREADS) {
+                const int row = i / (BK / 8), kk = (i % (BK / 8)) * 8;
+                const bool ok = k0 + kk < p.k;
+                moe_copy16(&As[st][row][kk], A + (size_t)arow[row] * p.k + (ok ? k0 + kk : 0), ok);
             }
-            for (int i = tid; i < GN * (GK / 8); i += GEMM_THREADS) {
-                const int col = i / (GK / 8), kk = (i % (GK / 8)) * 8;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (n0 + col < p.n && k0 + kk < p.k) v = *reinterpret_cast<const uint4*>(W + (size_t)(n0 + col) * p.k + k0 + kk);
-                *reinterpret_cast<uint4*>(&Ws[col][kk]) = v;
+            for (int i = tid; i < GN * (BK / 8); i += GEMM_THREADS) {
+                const int col = i / (BK / 8), kk = (i % (BK / 8)) * 8;
+                const bool ok = n0 + col < p.n && k0 + kk < p.k;
+                moe_copy16(&Ws[st][col][kk], W + (ok ? (size_t)(n0 + col) * p.k + k0 + kk : 0), ok);
             }
         } else {
-            for (int i = tid; i < GM * GK; i += GEMM_THREADS) {
-                const int row = i / GK, kk = i % GK;
-                As[row][kk] = (k0 + kk < p.k) ? A[(size_t)arow[row] * p.k + k0 + kk] : __float2bfloat16_rn(0.f);
+            for (int i = tid; i < GM * BK; i += GEMM_THREADS) {
+                const int row = i / BK, kk = i % BK;
+                As[st][row][kk] = (k0 + kk < p.k) ? A[(size_t)arow[row] * p.k + k0 + kk] : __float2bfloat16_rn(0.f);
             }
-            for (int i = tid; i < GN * GK; i += GEMM_THREADS) {
-                const int col = i / GK, kk = i % GK;
-                Ws[col][kk] = (n0 + col < p.n && k0 + kk < p.k) ? W[(size_t)(n0 + col) * p.k + k0 + kk] : __float2bfloat16_rn(0.f);
+            for (int i = tid; i < GN * BK; i += GEMM_THREADS) {
+                const int col = i / BK, kk = i % BK;
+                Ws[st][col][kk] = (n0 + col < p.n && k0 + kk < p.k) ? W[(size_t)(n0 + col) * p.k + k0 + kk] : __float2bfloat16_rn(0.f);
             }
         }
-        __syncthreads();
+    };
+    float acc[2][2][4] = {};
+    const int grp = lane >> 2, qd = lane & 3;
 #pragma unroll
-        for (int ks = 0; ks < GK; ks += 16) {
+    for (int st = 0; st < BSTAGES - 1; ++st) {
+        if (st < nk) load_stage(st, st);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int kt = 0; kt < nk; ++kt) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(BSTAGES - 2) : "memory");
+        __syncthreads();                                      // tile kt has landed; everyone is done with tile kt - 1
+        if (kt + BSTAGES - 1 < nk) load_stage(kt + BSTAGES - 1, (kt + BSTAGES - 1) % BSTAGES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int st = kt % BSTAGES;
+#pragma unroll
+        for (int ks = 0; ks < BK; ks += 16) {
             uint32_t af[2][4], bfr[2][2];
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt) {
                 const int r0 = mt * 16 + grp;
-                af[mt][0] = *reinterpret_cast<const uint32_t*>(&As[r0][ks + qd * 2]);
-                af[mt][1] = *reinterpret_cast<const uint32_t*>(&As[r0 + 8][ks + qd * 2]);
-                af[mt][2] = *reinterpret_cast<const uint32_t*>(&As[r0][ks + qd * 2 + 8]);
-                af[mt][3] = *reinterpret_cast<const uint32_t*>(&As[r0 + 8][ks + qd * 2 + 8]);
+                af[mt][0] = *reinterpret_cast<const uint32_t*>(&As[st][r0][ks + qd * 2]);
+                af[mt][1] = *reinterpret_cast<const uint32_t*>(&As[st][r0 + 8][ks + qd * 2]);
+                af[mt][2] = *reinterpret_cast<const uint32_t*>(&As[st][r0][ks + qd * 2 + 8]);
+                af[mt][3] = *reinterpret_cast<const uint32_t*>(&As[st][r0 + 8][ks + qd * 2 + 8]);
             }
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const int c0 = warp * 16 + nt * 8 + grp;
-                bfr[nt][0] = *reinterpret_cast<const uint32_t*>(&Ws[c0][ks + qd * 2]);
-                bfr[nt][1] = *reinterpret_cast<const uint32_t*>(&Ws[c0][ks + qd * 2 + 8]);
+                bfr[nt][0] = *reinterpret_cast<const uint32_t*>(&Ws[st][c0][ks + qd * 2]);
+                bfr[nt][1] = *reinterpret_cast<const uint32_t*>(&Ws[st][c0][ks + qd * 2 + 8]);
             }
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt)
@@ -313,8 +335,8 @@ moe_grouped_bf16_kernel(const GroupedParams p) {
                         : "+f"(acc[mt][nt][0]), "+f"(acc[mt][nt][1]), "+f"(acc[mt][nt][2]), "+f"(acc[mt][nt][3])
                         : "r"(af[mt][0]), "r"(af[mt][1]), "r"(af[mt][2]), "r"(af[mt][3]), "r"(bfr[nt][0]), "r"(bfr[nt][1]));
         }
-        __syncthreads();
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     TO* out = static_cast<TO*>(p.out);
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)

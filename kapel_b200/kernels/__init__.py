@@ -729,13 +729,15 @@ def entry_ranges(row_entry: torch.Tensor, entries: int):
 
 
 MLSTM_SLICE = 16          # value components a block of the scan kernel holds (the kernel file's MV)
+MLSTM_SHARE = 8           # threads that share a value component (its MJ)
 
 
 def mlstm_state_floats(d: int, e: int) -> int:
-    """Floats a head keeps between steps: the memory [d, e], and the normaliser [d] and the running
-    maximum once for every slice of value components the scan kernel cuts a head into. Plain
-    arithmetic (a cache is sized without the CUDA library); `mlstm_scan` checks it against the library's."""
-    return d * e + -(-e // MLSTM_SLICE) * (d + 1)
+    """Floats a head keeps between steps: for every slice of value components the scan kernel cuts
+    a head into, the memory's rows in the order of the threads that hold them, and a copy of the
+    normaliser [d] and of the running maximum. Plain arithmetic (a cache is sized without the CUDA
+    library); `mlstm_scan` checks it against the library's."""
+    return -(-e // MLSTM_SLICE) * (-(-d // MLSTM_SHARE) * MLSTM_SLICE * MLSTM_SHARE + d + 1)
 
 
 def mlstm_scan(stacked, q_off: int, k_off: int, v_off: int, i_off: int, f_off: int, bias_i, bias_f, state, ranges, slots,
@@ -882,7 +884,7 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, uni
 # events and its device time added up under its name and its largest argument's shape.
 _TIMED = ("embed", "rope_table", "rope_append", "glu", "cast", "gather_rows", "rmsnorm", "add_rmsnorm", "gemm",
           "paged_attention_rows", "paged_attention_mma", "sample", "proj_norm_append", "head_gate", "mlstm_scan", "moe_route",
-          "moe_sort", "moe_grouped", "moe_combine")
+          "moe_sort", "moe_grouped", "moe_combine", "gemm_glu_fused", "paged_attention_decode_fused")
 _timing = None
 _originals = {}
 

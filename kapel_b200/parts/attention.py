@@ -45,11 +45,8 @@ class Attention(Part):
             raise ValueError(f"attention: {spec.num_heads} heads over {spec.num_kv_heads} kv heads")
         self.v_dim = spec.v_head_dim or spec.head_dim
         self.general = bool(spec.gated or spec.q_norm or spec.k_norm or spec.keep_first or self.v_dim != spec.head_dim)
-        piece = 16 if not self.general else (4 if ctx.is_f32 else 8)
-        if spec.head_dim % piece:
-            raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of {piece} for the kernels")
-        if self.v_dim % 2:
-            raise ValueError(f"attention: the values' size {self.v_dim} must be even for the kernels")
+        if not self.general and spec.head_dim % 16:
+            raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16 for the kernels")
         if spec.keep_first < 0 or (spec.keep_first and not spec.window):
             raise ValueError(f"attention: {spec.keep_first} first keys kept with window {spec.window}")
         for n, width in ((spec.q_norm, spec.num_heads * spec.head_dim), (spec.k_norm, spec.num_kv_heads * spec.head_dim)):
