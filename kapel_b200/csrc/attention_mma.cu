@@ -57,6 +57,7 @@ struct AttMmaParams {
     float* partial;            // [rows, hq, slots, d + 2] when slots > 1
     int rows, hq, hkv, d, page_size, table_width, n_pages;
     int window, split, slots;
+    int keep;                  // with a window: keys [0, keep) stay visible below it (prompt kernel only, one slot)
     int decode_bar_offset;     // bytes from the start of shared memory to the decode kernel's mbarriers
     int direct;                // 1: a row whose keys all lie in one slot was written to `out` by that slot's block
     int relative;              // 1: every request brings one token (tile t = row t = request t) and slots are counted from the row's first visible key, else from key 0
@@ -312,7 +313,7 @@ template <int HD, bool FULL>
 __device__ __forceinline__ void am_tile_boxes(const bf16* q16, uint32_t tK, uint32_t tV, int ld, int d, int nbox, int j0,
                                               const int (&cnt)[2], const int (&fst)[2], int fst_hi, int cnt_lo, int klo,
                                               int khi, float sc, float cap, float (&o)[HD / 8][4], float (&m_run)[2],
-                                              float (&l_run)[2], int lane) {
+                                              float (&l_run)[2], int lane, int keep = 0) {
     constexpr int NKEYS = 64;
     constexpr int NT_S = NKEYS / 8;
     constexpr int NT_O = HD / 8;
@@ -349,7 +350,7 @@ __device__ __forceinline__ void am_tile_boxes(const bf16* q16, uint32_t tK, uint
             if (cap > 0.f) v = cap * am_tanh(v);
             if (!inner) {
                 const int j = j0 + nt * 8 + t * 2 + (e & 1);
-                const bool seen = j >= fst[h] && j < cnt[h] && j >= klo && j < khi;
+                const bool seen = ((j >= fst[h] && j >= klo) || j < keep) && j < cnt[h] && j < khi;
                 v = seen ? v : -INFINITY;
             }
             s[nt][e] = v;
@@ -441,7 +442,11 @@ attention_mma_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap m
         return;
     }
     const int k_begin = klo / AM_KT * AM_KT;               // tiles are cut at multiples of KT
-    const int n_tiles = (khi - k_begin + AM_KT - 1) / AM_KT;
+    // Kept first keys below the window's first tile come as tiles of their own ahead of the window's.
+    const int keep = p.keep;
+    const int n_keep = keep > 0 ? (min(keep, k_begin) + AM_KT - 1) / AM_KT : 0;
+    const int n_tiles = n_keep + (khi - k_begin + AM_KT - 1) / AM_KT;
+    auto tile_pos = [&](int kt) { return kt < n_keep ? kt * AM_KT : k_begin + (kt - n_keep) * AM_KT; };
 
     if (tid == 0) {
         am_mbar_init(bars, 1);
@@ -459,10 +464,10 @@ attention_mma_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap m
     // The pages of tile kt's four groups of 16 keys, written one iteration ahead by four threads.
     auto find_pages = [&](int kt) {
         if (tid < 4) {
-            const int j = k_begin + kt * AM_KT + tid * 16;
+            const int j = tile_pos(kt) + tid * 16;
             int page = -1;
-            if (kt < n_tiles && j < khi && j + 16 > klo) {
-                const int lp = max(j, klo) / p.page_size;
+            if (kt < n_tiles && j < khi && (j + 16 > klo || j < keep)) {
+                const int lp = (j < keep ? j : max(j, klo)) / p.page_size;
                 if (lp < p.table_width) page = p.block_table[(size_t)x.entry * p.table_width + lp];
                 if (page >= p.n_pages) page = -1;
             }
@@ -486,7 +491,7 @@ attention_mma_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap m
                 const int sub = op / (2 * nbox), bx = op % (2 * nbox);
                 const int page = pages[sub];
                 if (page < 0) continue;
-                const int j = k_begin + kt * AM_KT + sub * 16;
+                const int j = tile_pos(kt) + sub * 16;
                 const int row = (page * p.hkv + kvh) * p.page_size + j % p.page_size;
                 if (bx < nbox) am_tma_box(dst + (uint32_t)(sub * nbox + bx) * 2048u, &map_k, bx * 64, row, bars + stage);
                 else am_tma_box(dst + half_bytes + (uint32_t)(sub * nbox + bx - nbox) * 2048u, &map_v, (bx - nbox) * 64, row, bars + stage);
@@ -531,8 +536,8 @@ attention_mma_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap m
         if (kt + 1 < n_tiles) load_tile(kt + 1);
         find_pages(kt + 2);                                 // read after the next barrier; last read before this one
         const uint32_t tk = stages + (uint32_t)(kt & 1) * stage_bytes;
-        am_tile_boxes<HD, FULL>(sQ + wrow * ld, tk, tk + half_bytes, ld, d, nbox, k_begin + kt * AM_KT, cnt, fst, fst_hi, cnt_lo,
-                                klo, khi, sc, p.cap, o, m_run, l_run, lane);
+        am_tile_boxes<HD, FULL>(sQ + wrow * ld, tk, tk + half_bytes, ld, d, nbox, tile_pos(kt), cnt, fst, fst_hi, cnt_lo,
+                                klo, khi, sc, p.cap, o, m_run, l_run, lane, keep);
     }
     if (failed) {
         if (tid == 0) atomicExch(&g_attention_error, 1);
@@ -1336,7 +1341,7 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
                                 const int* block_table, const int* row_count, const int* tile_entry,
                                 const int* tile_row0, const int* tile_nq, int tiles, int rows, int hq, int hkv, int d,
                                 int page_size, int table_width, int n_pages, int window, int split, int slots,
-                                float scale, float cap, int decode, int relative, float* scratch, void* stream) {
+                                float scale, float cap, int decode, int relative, int keep, float* scratch, void* stream) {
     // decode: 0 for prompt portions; else the most rows (tokens x query heads of a kv head) any tile
     // holds, at most 16.
     KB_REQUIRE(rows >= 0 && tiles >= 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_mma: rows %d, tiles %d, heads %d over %d", rows, tiles, hq, hkv);
@@ -1352,8 +1357,11 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     KB_REQUIRE(relative == 0 || relative == 1, "attention_mma: relative %d (0 or 1: slots counted from each tile's first visible key, for tiles of one token)", relative);
     KB_REQUIRE(!(decode && relative) || tiles == rows, "attention_mma: relative with %d tiles for %d rows (every request brings one token: tile t is row t of request t)", tiles, rows);
     KB_REQUIRE(hkv <= 65535, "attention_mma: %d kv heads is too many for one launch", hkv);
+    KB_REQUIRE(keep >= 0 && (keep == 0 || (window > 0 && !decode && split == 0 && slots == 1)),
+               "attention_mma: %d first keys kept need a window, prompt portions and one slot", keep);
     if (rows == 0 || tiles == 0) return 0;
     AttMmaParams p;
+    p.keep = keep;
     p.q = (const bf16*)q; p.k_table = (const bf16*)k_table; p.v_table = (const bf16*)v_table;
     p.block_table = block_table; p.row_count = row_count; p.tile_entry = tile_entry; p.tile_row0 = tile_row0;
     p.tile_nq = tile_nq; p.out = (bf16*)out; p.partial = slots > 1 ? scratch : nullptr;
@@ -1397,6 +1405,7 @@ extern "C" int kb_attention_decode_fused(void* out, const float* qkv_parts, int 
     KB_REQUIRE(hkv <= 65535, "attention_decode_fused: %d kv heads is too many for one launch", hkv);
     if (rows == 0) return 0;
     AttMmaParams p;
+    p.keep = 0;
     p.q = nullptr; p.k_table = (const bf16*)k_table; p.v_table = (const bf16*)v_table;
     p.block_table = block_table; p.row_count = row_count; p.tile_entry = nullptr; p.tile_row0 = nullptr;
     p.tile_nq = nullptr; p.out = (bf16*)out; p.partial = slots > 1 ? scratch : nullptr;

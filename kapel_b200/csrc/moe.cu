@@ -113,7 +113,8 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, con
 }
 
 // ------------------------------------------------------------------------------------------- sort
-constexpr int GM = 32;         // rows of a grouped product's tile
+constexpr int GM = 32;         // rows of a grouped product's tile: few rows an expert, and the 32-bit path
+constexpr int GM_LARGE = 64;   // and where an expert has many rows (bfloat16)
 constexpr int SORT_THREADS = 1024;
 
 // One block. offsets [E + 1]; order [pairs]: pair numbers by expert (any order within an expert);
@@ -121,7 +122,7 @@ constexpr int SORT_THREADS = 1024;
 __global__ void __launch_bounds__(SORT_THREADS)
 moe_sort_kernel(const int* __restrict__ experts, int pairs, int n_experts, int* __restrict__ offsets, int* __restrict__ order,
                 int* __restrict__ tile_expert, int* __restrict__ tile_first, int* __restrict__ tile_rows, int* __restrict__ n_tiles,
-                int tile_cap) {
+                int tile_cap, int rows_a_tile) {
     extern __shared__ int si[];
     int* count = si;                 // [E]
     int* cursor = si + n_experts;    // [E]
@@ -137,11 +138,11 @@ moe_sort_kernel(const int* __restrict__ experts, int pairs, int n_experts, int* 
         for (int x = 0; x < n_experts; ++x) {
             offsets[x] = at;
             cursor[x] = at;
-            for (int t = 0; t < count[x]; t += GM) {
+            for (int t = 0; t < count[x]; t += rows_a_tile) {
                 if (tiles < tile_cap) {
                     tile_expert[tiles] = x;
                     tile_first[tiles] = at + t;
-                    tile_rows[tiles] = min(GM, count[x] - t);
+                    tile_rows[tiles] = min(rows_a_tile, count[x] - t);
                 }
                 ++tiles;
             }
@@ -237,11 +238,11 @@ moe_grouped_f32_kernel(const GroupedParams p) {
     }
 }
 
-// bfloat16 operands, 32-bit sums by mma.sync m16n8k16; four warps, each all 32 rows x 16 columns.
-// Tiles of BK k values arrive by 16-byte asynchronous copies, three stages deep, so that a block
-// that walks one expert's weights for a handful of rows (a decoding step) keeps loads in flight
-// instead of waiting for each tile; rows of k that are no multiple of 8 are loaded value by value.
-constexpr int BK = 64;
+// bfloat16 operands, 32-bit sums by mma.sync m16n8k16. A block takes TM rows of one expert by TN
+// columns with WM x WN warps; tiles of TK k values arrive by 16-byte asynchronous copies, three
+// stages deep, so that a block that walks one expert's weights for a handful of rows (a decoding
+// step) keeps loads in flight instead of waiting for each tile; rows of k that are no multiple of
+// 8 are loaded value by value. Two shapes: 32 x 64 (few rows an expert) and 64 x 128 (prompts).
 constexpr int BSTAGES = 3;
 
 __device__ __forceinline__ void moe_copy16(void* dst, const void* src, bool valid) {
@@ -250,18 +251,21 @@ __device__ __forceinline__ void moe_copy16(void* dst, const void* src, bool vali
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d32), "l"(src), "r"(bytes) : "memory");
 }
 
-template <typename TO>
-__global__ void __launch_bounds__(GEMM_THREADS)
+template <typename TO, int TM, int TN, int WM, int WN, int TK>
+__global__ void __launch_bounds__(WM * WN * 32)
 moe_grouped_bf16_kernel(const GroupedParams p) {
+    constexpr int THREADS = WM * WN * 32;
+    constexpr int MT = TM / WM / 16, NT = TN / WN / 8;       // m16 and n8 tiles a warp
     const int tile = blockIdx.x;
     if (tile >= p.n_tiles[0]) return;
-    __shared__ __align__(16) bf16 As[BSTAGES][GM][BK + 8];
-    __shared__ __align__(16) bf16 Ws[BSTAGES][GN][BK + 8];
-    __shared__ int arow[GM], orow[GM];
+    __shared__ __align__(16) bf16 As[BSTAGES][TM][TK + 8];
+    __shared__ __align__(16) bf16 Ws[BSTAGES][TN][TK + 8];
+    __shared__ int arow[TM], orow[TM];
     const int expert = p.tile_expert[tile], first = p.tile_first[tile], nrows = p.tile_rows[tile];
-    const int n0 = blockIdx.y * GN;
+    const int n0 = blockIdx.y * TN;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid < GM) {
+    const int wm = warp / WN, wn = warp % WN;
+    if (tid < TM) {
         const int place = first + min(tid, nrows - 1);
         const int pair = p.order[place];
         arow[tid] = p.a_by ? pair / p.top : place;
@@ -271,32 +275,32 @@ moe_grouped_bf16_kernel(const GroupedParams p) {
     const bf16* A = static_cast<const bf16*>(p.a);
     const bf16* W = static_cast<const bf16*>(p.w) + (size_t)expert * p.n * p.k;
     const bool vec = (p.k % 8) == 0 && ((((uintptr_t)A) | ((uintptr_t)W)) & 15) == 0;
-    const int nk = (p.k + BK - 1) / BK;
+    const int nk = (p.k + TK - 1) / TK;
     auto load_stage = [&](int kt, int st) {
-        const int k0 = kt * BK;
+        const int k0 = kt * TK;
         if (vec) {
-            for (int i = tid; i < GM * (BK / 8); i += GEMM_THREADS) {
-                const int row = i / (BK / 8), kk = (i % (BK / 8)) * 8;
+            for (int i = tid; i < TM * (TK / 8); i += THREADS) {
+                const int row = i / (TK / 8), kk = (i % (TK / 8)) * 8;
                 const bool ok = k0 + kk < p.k;
                 moe_copy16(&As[st][row][kk], A + (size_t)arow[row] * p.k + (ok ? k0 + kk : 0), ok);
             }
-            for (int i = tid; i < GN * (BK / 8); i += GEMM_THREADS) {
-                const int col = i / (BK / 8), kk = (i % (BK / 8)) * 8;
+            for (int i = tid; i < TN * (TK / 8); i += THREADS) {
+                const int col = i / (TK / 8), kk = (i % (TK / 8)) * 8;
                 const bool ok = n0 + col < p.n && k0 + kk < p.k;
                 moe_copy16(&Ws[st][col][kk], W + (ok ? (size_t)(n0 + col) * p.k + k0 + kk : 0), ok);
             }
         } else {
-            for (int i = tid; i < GM * BK; i += GEMM_THREADS) {
-                const int row = i / BK, kk = i % BK;
+            for (int i = tid; i < TM * TK; i += THREADS) {
+                const int row = i / TK, kk = i % TK;
                 As[st][row][kk] = (k0 + kk < p.k) ? A[(size_t)arow[row] * p.k + k0 + kk] : __float2bfloat16_rn(0.f);
             }
-            for (int i = tid; i < GN * BK; i += GEMM_THREADS) {
-                const int col = i / BK, kk = i % BK;
+            for (int i = tid; i < TN * TK; i += THREADS) {
+                const int col = i / TK, kk = i % TK;
                 Ws[st][col][kk] = (n0 + col < p.n && k0 + kk < p.k) ? W[(size_t)(n0 + col) * p.k + k0 + kk] : __float2bfloat16_rn(0.f);
             }
         }
     };
-    float acc[2][2][4] = {};
+    float acc[MT][NT][4] = {};
     const int grp = lane >> 2, qd = lane & 3;
 #pragma unroll
     for (int st = 0; st < BSTAGES - 1; ++st) {
@@ -310,26 +314,26 @@ moe_grouped_bf16_kernel(const GroupedParams p) {
         asm volatile("cp.async.commit_group;" ::: "memory");
         const int st = kt % BSTAGES;
 #pragma unroll
-        for (int ks = 0; ks < BK; ks += 16) {
-            uint32_t af[2][4], bfr[2][2];
+        for (int ks = 0; ks < TK; ks += 16) {
+            uint32_t af[MT][4], bfr[NT][2];
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
-                const int r0 = mt * 16 + grp;
+            for (int mt = 0; mt < MT; ++mt) {
+                const int r0 = wm * (TM / WM) + mt * 16 + grp;
                 af[mt][0] = *reinterpret_cast<const uint32_t*>(&As[st][r0][ks + qd * 2]);
                 af[mt][1] = *reinterpret_cast<const uint32_t*>(&As[st][r0 + 8][ks + qd * 2]);
                 af[mt][2] = *reinterpret_cast<const uint32_t*>(&As[st][r0][ks + qd * 2 + 8]);
                 af[mt][3] = *reinterpret_cast<const uint32_t*>(&As[st][r0 + 8][ks + qd * 2 + 8]);
             }
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                const int c0 = warp * 16 + nt * 8 + grp;
+            for (int nt = 0; nt < NT; ++nt) {
+                const int c0 = wn * (TN / WN) + nt * 8 + grp;
                 bfr[nt][0] = *reinterpret_cast<const uint32_t*>(&Ws[st][c0][ks + qd * 2]);
                 bfr[nt][1] = *reinterpret_cast<const uint32_t*>(&Ws[st][c0][ks + qd * 2 + 8]);
             }
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
+                for (int nt = 0; nt < NT; ++nt)
                     asm volatile(
                         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                         : "+f"(acc[mt][nt][0]), "+f"(acc[mt][nt][1]), "+f"(acc[mt][nt][2]), "+f"(acc[mt][nt][3])
@@ -339,13 +343,13 @@ moe_grouped_bf16_kernel(const GroupedParams p) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     TO* out = static_cast<TO*>(p.out);
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-                const int row = mt * 16 + grp + (v >= 2 ? 8 : 0);
-                const int col = n0 + warp * 16 + nt * 8 + qd * 2 + (v & 1);
+                const int row = wm * (TM / WM) + mt * 16 + grp + (v >= 2 ? 8 : 0);
+                const int col = n0 + wn * (TN / WN) + nt * 8 + qd * 2 + (v & 1);
                 if (row < nrows && col < p.n) Elem<TO>::store(out + (size_t)orow[row] * p.n + col, moe_act(acc[mt][nt][v], p.act));
             }
 }
@@ -367,7 +371,10 @@ __global__ void moe_combine_kernel(TO* __restrict__ out, const float* __restrict
 
 using namespace kb;
 
-extern "C" int kb_moe_tile_rows() { return GM; }
+// Rows of a grouped product's tile when an expert has about `rows_an_expert` rows.
+extern "C" int kb_moe_tile_rows(int dt, long long rows_an_expert) {
+    return (dt == KB_DT_BF16 && rows_an_expert >= 48) ? GM_LARGE : GM;
+}
 
 extern "C" int kb_moe_route(int* experts, float* weights, const void* h, int h_dt, const float* router, const float* correction,
                             int rows, int width, int n_experts, int top, int groups, int keep_groups, int group_top,
@@ -392,26 +399,29 @@ extern "C" int kb_moe_route(int* experts, float* weights, const void* h, int h_d
 }
 
 extern "C" int kb_moe_sort(const int* experts, int pairs, int n_experts, int* offsets, int* order, int* tile_expert,
-                           int* tile_first, int* tile_rows, int* n_tiles, int tile_cap, void* stream) {
+                           int* tile_first, int* tile_rows, int* n_tiles, int tile_cap, int rows_a_tile, void* stream) {
     KB_REQUIRE(pairs >= 0 && n_experts > 0 && tile_cap >= 0, "moe_sort: %d pairs, %d experts", pairs, n_experts);
+    KB_REQUIRE(rows_a_tile == GM || rows_a_tile == GM_LARGE, "moe_sort: tiles of %d rows (%d or %d)", rows_a_tile, GM, GM_LARGE);
     const size_t smem = (size_t)2 * n_experts * sizeof(int);
     KB_REQUIRE(smem <= 48 * 1024, "moe_sort: %d experts are too many", n_experts);
     moe_sort_kernel<<<1, SORT_THREADS, smem, (cudaStream_t)stream>>>(experts, pairs, n_experts, offsets, order, tile_expert, tile_first,
-                                                                    tile_rows, n_tiles, tile_cap);
+                                                                    tile_rows, n_tiles, tile_cap, rows_a_tile);
     return check_launch("moe_sort");
 }
 
 // act: 0 none, 1 relu squared, 2 gelu_tanh, 3 silu.
 extern "C" int kb_moe_grouped(void* out, int out_dt, const void* a, const void* w, int dt, const int* order, const int* tile_expert,
-                              const int* tile_first, const int* tile_rows, const int* n_tiles, int tile_cap, int n, int k, int top,
-                              int act, int a_by_token, int out_by_pair, void* stream) {
+                              const int* tile_first, const int* tile_rows, const int* n_tiles, int tile_cap, int rows_a_tile, int n,
+                              int k, int top, int act, int a_by_token, int out_by_pair, void* stream) {
     KB_REQUIRE(n > 0 && k > 0 && top > 0 && tile_cap >= 0, "moe_grouped: n %d, k %d, top %d", n, k, top);
+    KB_REQUIRE(rows_a_tile == GM || (rows_a_tile == GM_LARGE && dt == KB_DT_BF16), "moe_grouped: tiles of %d rows", rows_a_tile);
     KB_REQUIRE(act >= 0 && act <= 3, "moe_grouped: activation code %d is not known", act);
     if (tile_cap == 0) return 0;
     GroupedParams p;
     p.a = a; p.w = w; p.out = out; p.order = order; p.tile_expert = tile_expert; p.tile_first = tile_first; p.tile_rows = tile_rows;
     p.n_tiles = n_tiles; p.n = n; p.k = k; p.top = top; p.act = act; p.a_by = a_by_token; p.out_by = out_by_pair;
-    const int col_tiles = (n + GN - 1) / GN;
+    const int tn = rows_a_tile == GM_LARGE ? 128 : GN;
+    const int col_tiles = (n + tn - 1) / tn;
     KB_REQUIRE(col_tiles <= 65535, "moe_grouped: %d columns are too many for one launch", n);
     dim3 grid(tile_cap, col_tiles);
     cudaStream_t s = (cudaStream_t)stream;
@@ -419,9 +429,14 @@ extern "C" int kb_moe_grouped(void* out, int out_dt, const void* a, const void* 
         KB_REQUIRE(out_dt == KB_DT_F32, "moe_grouped: a 32-bit product writes 32-bit");
         moe_grouped_f32_kernel<<<grid, GEMM_THREADS, 0, s>>>(p);
     } else if (dt == KB_DT_BF16) {
-        if (out_dt == KB_DT_F32) moe_grouped_bf16_kernel<float><<<grid, GEMM_THREADS, 0, s>>>(p);
-        else if (out_dt == KB_DT_BF16) moe_grouped_bf16_kernel<bf16><<<grid, GEMM_THREADS, 0, s>>>(p);
-        else return fail("moe_grouped: output dtype code %d is not known", out_dt);
+        KB_REQUIRE(out_dt == KB_DT_F32 || out_dt == KB_DT_BF16, "moe_grouped: output dtype code %d is not known", out_dt);
+        if (rows_a_tile == GM_LARGE) {
+            if (out_dt == KB_DT_F32) moe_grouped_bf16_kernel<float, GM_LARGE, 128, 2, 4, 32><<<grid, 256, 0, s>>>(p);
+            else moe_grouped_bf16_kernel<bf16, GM_LARGE, 128, 2, 4, 32><<<grid, 256, 0, s>>>(p);
+        } else {
+            if (out_dt == KB_DT_F32) moe_grouped_bf16_kernel<float, GM, GN, 1, 4, 64><<<grid, 128, 0, s>>>(p);
+            else moe_grouped_bf16_kernel<bf16, GM, GN, 1, 4, 64><<<grid, 128, 0, s>>>(p);
+        }
     } else return fail("moe_grouped: dtype code %d is not known", dt);
     return check_launch("moe_grouped");
 }

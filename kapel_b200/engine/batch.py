@@ -189,15 +189,16 @@ class StepBatch:
             self.groups.append(GroupBatch(views[6 + 2 * i], views[7 + 2 * i].view(shape)))
 
     def attention_tiles(self, heads_per_kv: int, kv_heads: int, window: Optional[int] = None, head_dim: int = 256,
-                        prompt_kernel: str = "mma"):
+                        prompt_kernel: str = "mma", keep_first: int = 0):
         """How the tensor-core attention kernel cuts this step: (decode, (tile_entry, tile_row0,
         tile_nq) on the device, split, slots). `decode` is the most rows (tokens x query heads of a
         kv head) of any request when that is at most 16, which selects the decode kernel, else 0.
         The keys are split across blocks when the tiles alone are too few to fill the GPU;
         `prompt_kernel` names the kernel whose costs decide that for prompt portions. A fifth
         value says whether the slots are counted from each row's first visible key (every
-        request brings one token) or from key 0."""
-        key = ("tiles", heads_per_kv, kv_heads, window, head_dim, prompt_kernel)
+        request brings one token) or from key 0. With `keep_first` (keys that stay visible below
+        the window) prompt portions are not cut into slots."""
+        key = ("tiles", heads_per_kv, kv_heads, window, head_dim, prompt_kernel, keep_first)
         if key not in self.memo:
             from .. import kernels as K
 
@@ -217,6 +218,8 @@ class StepBatch:
             relative = bool(decode) and int(plan.q_len.max()) == 1
             if decode:
                 split, slots = decode_split(n * kv_heads, longest, sm_count(self.ids.device), window, relative)
+            elif keep_first and window:
+                split, slots = 0, 1
             else:
                 firsts = plan.row_count[arrays[1]]
                 split, slots = prompt_split(firsts, firsts + arrays[2] - 1, kv_heads, sm_count(self.ids.device), window,

@@ -77,7 +77,7 @@ class StaticBatch:
         return self.memo["entry_ranges"]
 
     def attention_tiles(self, heads_per_kv: int, kv_heads: int, window: Optional[int] = None, head_dim: int = 256,
-                        prompt_kernel: str = "mma"):
+                        prompt_kernel: str = "mma", keep_first: int = 0):
         if (kv_heads, window) not in self._mma:
             self._mma[(kv_heads, window)] = decode_split(self.rows * kv_heads, self._longest, sm_count(self._device), window, True)
         split, slots = self._mma[(kv_heads, window)]

@@ -612,14 +612,15 @@ def paged_attention_decode_fused(qkv: "SplitSum", cos_sin, lines, k_table, v_tab
 
 def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page_size: int, window: Optional[int],
                         scale: float, softcap: Optional[float], decode: int, split: int, slots: int,
-                        relative: bool = False, pairs: Optional[int] = None) -> torch.Tensor:
+                        relative: bool = False, pairs: Optional[int] = None, keep_first: int = 0) -> torch.Tensor:
     """Attention over the paged cache on tensor cores (bfloat16). `tiles` = (tile_entry, tile_row0,
     tile_nq) int32 device tensors: each tile is up to `attention_mma_rows(decode) // group` tokens of
     one request at consecutive positions. `decode` is 0 for prompt portions, else the most rows
     (tokens x query heads of a kv head) any tile holds, at most 16. `split` > 0 cuts the keys at
     absolute multiples of it over `slots` blocks (slots >= ceil(longest count / split)). With
     `relative` (decode mode, every tile one token) the multiples are counted from each row's first
-    visible key, so a windowed row needs ceil(window / split) slots however long its history."""
+    visible key, so a windowed row needs ceil(window / split) slots however long its history. With a
+    window, `keep_first` keys from position 0 stay visible below it (prompt portions in one slot only)."""
     rows, hq, d = q.shape
     _need(q, "attention q", torch.bfloat16)
     _need(k_table, "attention k table", torch.bfloat16)
@@ -637,7 +638,7 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
     lib = library()
     need = lib.kb_attention_mma_scratch_floats(rows, hq, d, int(slots))
     scratch = _fresh((need,), torch.float32, q.device) if need else None
-    if not decode and attention_prompt_kernel(hq, hkv, d, page_size, softcap) == "tcgen05":
+    if not decode and not keep_first and attention_prompt_kernel(hq, hkv, d, page_size, softcap) == "tcgen05":
         _check(
             lib.kb_attention_tc(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
                                 _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
@@ -652,7 +653,7 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
         lib.kb_attention_mma(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
                              _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
                              int(block_table.shape[1]), int(n_pages), int(window or 0), int(split), int(slots), _f(scale),
-                             _f(softcap or 0.0), int(decode), int(bool(relative) and bool(decode)), _ptr(scratch), _stream())
+                             _f(softcap or 0.0), int(decode), int(bool(relative) and bool(decode)), int(keep_first or 0), _ptr(scratch), _stream())
     )
     return out
 
@@ -728,16 +729,16 @@ def entry_ranges(row_entry: torch.Tensor, entries: int):
     return both[0], both[1]
 
 
-MLSTM_SLICE = 16          # value components a block of the scan kernel holds (the kernel file's MV)
-MLSTM_SHARE = 8           # threads that share a value component (its MJ)
+MLSTM_SLICE = 4           # value components a block of the scan kernel holds (the kernel file's MV)
+MLSTM_SHARE = 32          # threads that share a value component (its MJ)
 
 
 def mlstm_state_floats(d: int, e: int) -> int:
     """Floats a head keeps between steps: for every slice of value components the scan kernel cuts
-    a head into, the memory's rows in the order of the threads that hold them, and a copy of the
-    normaliser [d] and of the running maximum. Plain arithmetic (a cache is sized without the CUDA
+    a head into, the memory's rows in the order of the threads that hold them and a copy of the
+    normaliser [d]; then the running maximum, once. Plain arithmetic (a cache is sized without the CUDA
     library); `mlstm_scan` checks it against the library's."""
-    return -(-e // MLSTM_SLICE) * (-(-d // MLSTM_SHARE) * MLSTM_SLICE * MLSTM_SHARE + d + 1)
+    return -(-e // MLSTM_SLICE) * (-(-d // MLSTM_SHARE) * MLSTM_SLICE * MLSTM_SHARE + d) + 1
 
 
 def mlstm_scan(stacked, q_off: int, k_off: int, v_off: int, i_off: int, f_off: int, bias_i, bias_f, state, ranges, slots,
@@ -760,8 +761,9 @@ def mlstm_scan(stacked, q_off: int, k_off: int, v_off: int, i_off: int, f_off: i
     if min(start.numel(), end.numel(), slots.numel()) < entries:
         raise KernelError(f"mlstm: {entries} requests but ranges or slots for fewer")
     out = _fresh((rows, heads, e), torch.float32, src.device)
+    factors = _fresh((rows, heads, 3), torch.float32, src.device)        # the gates' kernel leaves every row's three factors here
     _check(library().kb_mlstm_scan(
-        _ptr(out), _ptr(src), dt, splits, ctypes.c_longlong(stride), width, int(q_off), int(k_off), int(v_off), int(i_off), int(f_off),
+        _ptr(out), _ptr(factors), _ptr(src), dt, splits, ctypes.c_longlong(stride), width, int(q_off), int(k_off), int(v_off), int(i_off), int(f_off),
         _ptr(bias_i), _ptr(bias_f), _ptr(state), int(state.shape[0]), _ptr(start), _ptr(end), _ptr(slots), int(entries), rows,
         heads, d, e, _f(cap), _f(q_scale), _f(floor), _stream()))
     return out
@@ -794,30 +796,23 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
     return experts, weights
 
 
-_MOE_TILE_ROWS = None
-
-
-def moe_tile_rows() -> int:
-    global _MOE_TILE_ROWS
-    if _MOE_TILE_ROWS is None:
-        _MOE_TILE_ROWS = int(library().kb_moe_tile_rows())
-    return _MOE_TILE_ROWS
-
-
 class ExpertLists:
     """The (token, k) pairs of a step listed by expert, and the row tiles of the grouped products."""
 
-    __slots__ = ("order", "offsets", "tiles", "tile_cap", "pairs", "top")
+    __slots__ = ("order", "offsets", "tiles", "tile_cap", "tile_rows", "pairs", "top")
 
 
-def moe_sort(experts: torch.Tensor, n_experts: int) -> ExpertLists:
+def moe_sort(experts: torch.Tensor, n_experts: int, dtype: torch.dtype = torch.float32) -> ExpertLists:
+    """Lists the pairs of `experts` [rows, top] by expert; `dtype` is the grouped products' (it and the
+    rows an expert gets on average decide how many rows a tile of those products has)."""
     _need(experts, "moe_sort experts", torch.int32)
     rows, top = experts.shape
     pairs = rows * top
     lists = ExpertLists()
     lists.pairs, lists.top = pairs, top
+    lists.tile_rows = int(library().kb_moe_tile_rows(_CODES[dtype], ctypes.c_longlong(pairs // max(n_experts, 1))))
     # every expert's list ends with at most one tile that is not full
-    lists.tile_cap = pairs // moe_tile_rows() + min(n_experts, pairs)
+    lists.tile_cap = pairs // lists.tile_rows + min(n_experts, pairs)
     buf = _fresh((n_experts + 1 + pairs + 3 * max(lists.tile_cap, 1) + 1,), torch.int32, experts.device)
     at = n_experts + 1
     lists.offsets, lists.order = buf[:at], buf[at : at + pairs]
@@ -825,7 +820,8 @@ def moe_sort(experts: torch.Tensor, n_experts: int) -> ExpertLists:
     cap = max(lists.tile_cap, 1)
     lists.tiles = (buf[at : at + cap], buf[at + cap : at + 2 * cap], buf[at + 2 * cap : at + 3 * cap], buf[at + 3 * cap :])
     _check(library().kb_moe_sort(_ptr(experts), pairs, int(n_experts), _ptr(lists.offsets), _ptr(lists.order), _ptr(lists.tiles[0]),
-                                 _ptr(lists.tiles[1]), _ptr(lists.tiles[2]), _ptr(lists.tiles[3]), int(lists.tile_cap), _stream()))
+                                 _ptr(lists.tiles[1]), _ptr(lists.tiles[2]), _ptr(lists.tiles[3]), int(lists.tile_cap),
+                                 int(lists.tile_rows), _stream()))
     return lists
 
 
@@ -844,7 +840,7 @@ def moe_grouped(a: torch.Tensor, w: torch.Tensor, lists: ExpertLists, act: str, 
     out = _fresh((lists.pairs, n), out_dtype, a.device)
     t = lists.tiles
     _check(library().kb_moe_grouped(_ptr(out), _CODES[out_dtype], _ptr(a), _ptr(w), _dt(a, "moe_grouped input"), _ptr(lists.order),
-                                    _ptr(t[0]), _ptr(t[1]), _ptr(t[2]), _ptr(t[3]), int(lists.tile_cap), n, k, int(lists.top),
+                                    _ptr(t[0]), _ptr(t[1]), _ptr(t[2]), _ptr(t[3]), int(lists.tile_cap), int(lists.tile_rows), n, k, int(lists.top),
                                     MOE_ACT_CODES[act], int(bool(a_by_token)), int(bool(out_by_pair)), _stream()))
     return out
 

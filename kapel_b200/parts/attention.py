@@ -85,9 +85,21 @@ class Attention(Part):
         group = batch.groups[cache.group]
         q = K.proj_norm_append(stacked, 0, nq, nq + nk, self.proj_norms[0], self.proj_norms[1], group.lines, k_table, v_table,
                                s.num_heads, s.num_kv_heads, s.head_dim, dv, cache.owns, self.ctx.dtype)
-        y = K.paged_attention_rows(
-            q, k_table, v_table, group.block_table, batch.row_entry, batch.row_count, self.ctx.page_size, s.window, s.scale,
-            s.softcap, batch.attention_slots(s.window, s.keep_first), s.keep_first)
+        heads_per_kv = s.num_heads // s.num_kv_heads
+        y = None
+        if dv == s.head_dim and K.attention_mma_takes(q.dtype, s.head_dim, heads_per_kv):
+            # prompt portions go to the tensor-core kernel, which knows the kept first keys; a pass of
+            # single tokens stays with the row-wise kernel below
+            decode, tiles, split, slots, _ = batch.attention_tiles(heads_per_kv, s.num_kv_heads, s.window, s.head_dim, "mma",
+                                                                   keep_first=s.keep_first if s.window else 0)
+            if not decode:
+                y = K.paged_attention_mma(q, k_table, v_table, group.block_table, batch.row_count, tiles, self.ctx.page_size,
+                                          s.window, s.scale, s.softcap, 0, split, slots, False,
+                                          keep_first=s.keep_first if s.window else 0)
+        if y is None:
+            y = K.paged_attention_rows(
+                q, k_table, v_table, group.block_table, batch.row_entry, batch.row_count, self.ctx.page_size, s.window, s.scale,
+                s.softcap, batch.attention_slots(s.window, s.keep_first), s.keep_first)
         if s.gated:
             y = K.head_gate(y, stacked, nq + nk + s.num_kv_heads * dv, None, False, 0.0, self.ctx.dtype)
         return linear(self.ctx, y.view(y.shape[0], s.num_heads * dv), self.w_o, keep_split=True)

@@ -55,7 +55,7 @@ class MoE(Part):
         s = self.spec
         experts, weights = K.moe_route(h, self.router, self.correction, s.top, s.groups, s.keep_groups, s.group_top, s.scoring,
                                        s.renormalize)
-        lists = K.moe_sort(experts, s.experts)
+        lists = K.moe_sort(experts, s.experts, self.w_up.dtype)
         if h.dtype != self.w_up.dtype:
             h = K.cast(h, self.w_up.dtype)
         inner = K.moe_grouped(h, self.w_up, lists, s.activation, True, False, self.w_up.dtype)

@@ -39,7 +39,7 @@ FUSITAR_A = {"architecture": "Fusitar", "vocab": 211, "width": 64, "embedding": 
 FUSITAR_B = {"architecture": "Fusitar", "vocab": 97, "width": 96, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-5}, "layers": [
     mlstm_layer(3, 16, 32, 15.0, moe(6, 1, 1, 1, 24)),
     mlstm_layer(1, 40, 24, 5.0, None),
-    attention_layer(6, 1, 32, 16, 0.125, 33, 5, moe(6, 2, 3, 2, 56)),
+    attention_layer(6, 1, 32, 32, 0.125, 33, 5, moe(6, 2, 3, 2, 56)),
 ]}
 CONFIGS = {"A": (FUSITAR_A, 11), "B": (FUSITAR_B, 12)}
 # Largest difference of logits over the largest plain logit. In 32-bit the runs see 2e-5; in bfloat16 (products
@@ -140,7 +140,8 @@ def dev(a, dtype=torch.float32):
 
 # --------------------------------------------------------------------------------- mechanisms alone
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hq,hkv,d,dv,size,keep", [(4, 2, 16, 24, 20, 3), (3, 1, 40, 10, 300, 270), (2, 2, 12, 7, 5, 0), (8, 1, 64, 64, 64, 17)])
+@pytest.mark.parametrize("hq,hkv,d,dv,size,keep", [(4, 2, 16, 24, 20, 3), (3, 1, 40, 10, 300, 270), (2, 2, 12, 7, 5, 0), (8, 1, 64, 64, 64, 17),
+                                                   (4, 2, 48, 48, 90, 130), (6, 3, 128, 128, 200, 1)])
 def test_attention_with_kept_first_keys_against_plain(dtype, hq, hkv, d, dv, size, keep):
     """The norm over the whole projections, the append and the attention kernel over shuffled pages,
     in two portions, against the plain mixer's pieces; lengths cross pages, the window and the chunk."""
@@ -180,19 +181,27 @@ def test_attention_with_kept_first_keys_against_plain(dtype, hq, hkv, d, dv, siz
         y = K.paged_attention_rows(qq, k_table, v_table, table, dev(np.zeros(b - a), torch.int32), dev(pos + 1, torch.int32),
                                    page, size, scale, None, slots, keep)
         got.append(y.float().cpu().numpy())
+        if dtype == torch.bfloat16 and d == dv and K.attention_mma_takes(dtype, d, hq // hkv):
+            # the same portion through the tensor-core kernel for prompt portions
+            from kapel_b200.engine.batch import cut_tiles
+
+            tiles = tuple(dev(t, torch.int32) for t in cut_tiles(np.asarray([0]), np.asarray([b - a]), K.attention_mma_rows(False) // (hq // hkv)))
+            z = K.paged_attention_mma(qq, k_table, v_table, table, dev(pos + 1, torch.int32), tiles, page, size, scale, None, 0, 0, 1,
+                                      keep_first=keep)
+            assert rel_err(z.float().cpu().numpy(), want[a:b]) < 3e-2
     err = rel_err(np.concatenate(got), want)
     assert err < (2e-5 if dtype == torch.float32 else 3e-2), err
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_a_window_and_its_kept_keys_are_exact_to_the_token(dtype):
+@pytest.mark.parametrize("dtype,dv", [(torch.float32, 8), (torch.bfloat16, 8), (torch.bfloat16, 16)])
+def test_a_window_and_its_kept_keys_are_exact_to_the_token(dtype, dv):
     """One key's score is made to stand out: the output is that key's value exactly when the plain
     rule says the query sees it. Keys just inside and just outside the window and the kept first
     tokens, at page borders and far back, for a prompt's rows and for a single decoded token."""
     from kapel_b200 import kernels as K
 
     hq = hkv = 1
-    d, dv, page, size, keep, T = 16, 8, 16, 37, 5, 420
+    d, page, size, keep, T = 16, 16, 37, 5, 420
     rng = np.random.default_rng(5)
     n_pages = -(-T // page)
     pages = rng.permutation(n_pages)
@@ -212,6 +221,13 @@ def test_a_window_and_its_kept_keys_are_exact_to_the_token(dtype):
         # as a prompt's rows, all at once
         rows = K.paged_attention_rows(q, k_table, v_table, table, dev(np.zeros(T), torch.int32), dev(pos + 1, torch.int32),
                                       page, size, 1.0, None, slots + T // K.attention_chunk(), keep).float().cpu().numpy()
+        ways = [rows]
+        if dtype == torch.bfloat16 and d == dv:               # and through the tensor-core kernel for prompt portions
+            from kapel_b200.engine.batch import cut_tiles
+
+            tiles = tuple(dev(t, torch.int32) for t in cut_tiles(np.asarray([0]), np.asarray([T]), K.attention_mma_rows(False)))
+            ways.append(K.paged_attention_mma(q, k_table, v_table, table, dev(pos + 1, torch.int32), tiles, page, size, 1.0, None, 0, 0, 1,
+                                              keep_first=keep).float().cpu().numpy())
         vt = v_table.float().cpu().numpy()
         stored = vt[pages[target // page], 0, target % page]
         for i in queries:
@@ -219,7 +235,7 @@ def test_a_window_and_its_kept_keys_are_exact_to_the_token(dtype):
             one = K.paged_attention_rows(q[i : i + 1].contiguous(), k_table, v_table, table, dev([0], torch.int32), dev([i + 1], torch.int32),
                                          page, size, 1.0, None, slots, keep).float().cpu().numpy()[0, 0]
             sees = PF.visible(i, target, size, keep)
-            for got in (rows[i, 0], one):
+            for got in [w[i, 0] for w in ways] + [one]:
                 hit = np.abs(got - stored).max() < 1e-3
                 assert hit == sees, f"query {i}, key {target}: visible {sees}, output follows the key {hit}"
 
@@ -318,7 +334,7 @@ def test_router_against_plain(experts, top, count, keep):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("rows,width,ff,experts,top", [(70, 40, 24, 6, 2), (1, 64, 100, 5, 5), (200, 24, 9, 3, 1)])
+@pytest.mark.parametrize("rows,width,ff,experts,top", [(70, 40, 24, 6, 2), (1, 64, 100, 5, 5), (200, 24, 9, 3, 1), (700, 72, 136, 4, 2)])
 def test_experts_against_plain(dtype, tol, rows, width, ff, experts, top):
     from kapel_b200 import kernels as K
 
@@ -333,7 +349,7 @@ def test_experts_against_plain(dtype, tol, rows, width, ff, experts, top):
     for i in range(rows):
         for x, w in zip(chosen[i], weights[i]):
             want[i] += w * (down[x] @ (np.maximum(up[x] @ h[i], 0.0) ** 2))
-    lists = K.moe_sort(dev(chosen, torch.int32), experts)
+    lists = K.moe_sort(dev(chosen, torch.int32), experts, dtype)
     inner = K.moe_grouped(dev(h, dtype), dev(up, dtype), lists, "relu2", True, False, dtype)
     y = K.moe_grouped(inner, dev(down, dtype), lists, "none", False, True, torch.float32)
     got = K.moe_combine(y, dev(weights), torch.float32).cpu().numpy()
