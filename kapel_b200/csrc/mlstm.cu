@@ -142,8 +142,9 @@ mlstm_scan_kernel(const Src<TS> src, const MlstmParams p) {
         n[i] = j < d ? st_n[j] : 0.f;
     }
 
-    const int tail = 2 * d;                                  // v [MV] | the three factors | padding
-    const int rowf = (2 * d + MV + 3 + 3) / 4 * 4;           // k [d] | q [d] | tail
+    constexpr int DP = R * MJ;                               // k and q padded to the threads' rows, zeros beyond d
+    constexpr int tail = 2 * DP;                             // v [MV] | the three factors | padding
+    constexpr int rowf = 2 * DP + 8;                         // k [DP] | q [DP] | tail
     bool async = false;
     if constexpr (sizeof(TS) == 4) async = src.splits == 1;
     // k and q as 16-byte pieces where every piece starts on a 16-byte boundary on both sides
@@ -153,20 +154,26 @@ mlstm_scan_kernel(const Src<TS> src, const MlstmParams p) {
         const int rbase = r0 + chunk * CH;
         const int nr = min(CH, r1 - rbase);
         float* base = staged + (size_t)buf * CH * rowf;
-        if (wide) {
-            const int pieces = d / 2;                        // 16-byte pieces of k and q together
-            for (int idx = tid; idx < nr * pieces; idx += MLSTM_THREADS) {
-                const int t = idx / pieces, x = (idx - t * pieces) * 4;
-                const size_t col = x < d ? (size_t)p.k_off + (size_t)head * d + x : (size_t)p.q_off + (size_t)head * d + (x - d);
-                mlstm_copy16(base + (size_t)t * rowf + x, reinterpret_cast<const float*>(src.p) + (size_t)(rbase + t) * p.row_width + col);
-            }
-        } else {
-            for (int idx = tid; idx < nr * 2 * d; idx += MLSTM_THREADS) {
-                const int t = idx / (2 * d), x = idx - t * 2 * d;
-                const size_t col = x < d ? (size_t)p.k_off + (size_t)head * d + x : (size_t)p.q_off + (size_t)head * d + (x - d);
-                const size_t at = (size_t)(rbase + t) * p.row_width + col;
-                if (async) mlstm_copy4(base + (size_t)t * rowf + x, reinterpret_cast<const float*>(src.p) + at);
-                else base[(size_t)t * rowf + x] = src.at(at);
+        // a warp a row in turn; its lanes walk the row's k, then its q
+        for (int t = tid / 32; t < nr; t += MLSTM_THREADS / 32) {
+            float* row = base + (size_t)t * rowf;
+            const size_t at = (size_t)(rbase + t) * p.row_width + (size_t)head * d;
+            const float* g = reinterpret_cast<const float*>(src.p);
+            if (wide) {
+                for (int x = (tid & 31) * 4; x < d; x += 128) {
+                    mlstm_copy16(row + x, g + at + p.k_off + x);
+                    mlstm_copy16(row + DP + x, g + at + p.q_off + x);
+                }
+            } else {
+                for (int x = tid & 31; x < d; x += 32) {
+                    if (async) {
+                        mlstm_copy4(row + x, g + at + p.k_off + x);
+                        mlstm_copy4(row + DP + x, g + at + p.q_off + x);
+                    } else {
+                        row[x] = src.at(at + p.k_off + x);
+                        row[DP + x] = src.at(at + p.q_off + x);
+                    }
+                }
             }
         }
         for (int idx = tid; idx < nr * (MV + 3); idx += MLSTM_THREADS) {
@@ -186,6 +193,12 @@ mlstm_scan_kernel(const Src<TS> src, const MlstmParams p) {
         }
         if (async) asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    if (d < DP) {                                            // the padding of k and q, once: no copy ever writes it
+        for (int idx = tid; idx < 2 * CH * 2 * (DP - d); idx += MLSTM_THREADS) {
+            const int t = idx / (2 * (DP - d)), x = idx - t * 2 * (DP - d);
+            staged[(size_t)t * rowf + (x < DP - d ? d + x : DP + d + (x - (DP - d)))] = 0.f;
+        }
+    }
     const int chunks = (r1 - r0 + CH - 1) / CH;
     stage(0, 0);
     for (int ch = 0; ch < chunks; ++ch) {
@@ -208,9 +221,8 @@ mlstm_scan_kernel(const Src<TS> src, const MlstmParams p) {
             float acc[2] = {0.f, 0.f}, nq[2] = {0.f, 0.f};     // two chains each, rows in turn
 #pragma unroll
             for (int i = 0; i < R; ++i) {
-                const int j = jg + i * MJ;
-                const float kk = j < d ? in[j] : 0.f;
-                const float q = j < d ? in[d + j] * p.q_scale : 0.f;
+                const float kk = in[jg + i * MJ];
+                const float q = in[DP + jg + i * MJ] * p.q_scale;
                 S[i] = fmaf(fa, S[i], kk * bv);
                 n[i] = fmaf(fa, n[i], fb * kk);
                 acc[i & 1] = fmaf(S[i], q, acc[i & 1]);
@@ -222,7 +234,7 @@ mlstm_scan_kernel(const Src<TS> src, const MlstmParams p) {
                 a += __shfl_xor_sync(0xffffffffu, a, o);
                 b += __shfl_xor_sync(0xffffffffu, b, o);
             }
-            if (live && jg == 0) p.out[((size_t)(rbase + t) * p.heads + head) * e + c] = a / (fmaxf(fabsf(b), em) + p.floor_);
+            if (live && jg == 0) p.out[((size_t)(rbase + t) * p.heads + head) * e + c] = a * __frcp_rn(fmaxf(fabsf(b), em) + p.floor_);
         }
         __syncthreads();                                     // the chunk's buffer may be written again
         if (!async && ch + 1 < chunks) stage(ch + 1, (ch + 1) & 1);
@@ -267,12 +279,11 @@ extern "C" int kb_mlstm_scan(float* out, float* factors, const void* src, int in
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(entries, heads, slices);
     const int need = (d + MJ - 1) / MJ;
-    const size_t rowf = (size_t)(2 * d + MV + 3 + 3) / 4 * 4;
 #define KB_MLSTM(TS, R, CH)                                                                                                     \
     do {                                                                                                                        \
         mlstm_gates_kernel<TS><<<dim3(entries, heads), 32, 0, s>>>(Src<TS>{(const TS*)src, splits, (size_t)split_stride}, p);     \
         if (int err = check_launch("mlstm gates")) return err;                                                                  \
-        mlstm_scan_kernel<TS, R, CH><<<grid, MLSTM_THREADS, 2 * CH * rowf * sizeof(float), s>>>(                                 \
+        mlstm_scan_kernel<TS, R, CH><<<grid, MLSTM_THREADS, (size_t)2 * CH * (2 * R * MJ + 8) * sizeof(float), s>>>(             \
             Src<TS>{(const TS*)src, splits, (size_t)split_stride}, p);                                                          \
     } while (0)
 #define KB_MLSTM_R(TS)                            \

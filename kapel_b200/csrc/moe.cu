@@ -18,7 +18,7 @@ namespace kb {
 typedef __nv_bfloat16 bf16;
 
 // ------------------------------------------------------------------------------------------ route
-constexpr int ROUTE_THREADS = 128;
+constexpr int ROUTE_THREADS = 256;
 
 template <typename TH>
 __global__ void __launch_bounds__(ROUTE_THREADS)
@@ -35,8 +35,19 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, con
     const TH* hr = h + (size_t)r * width;
     for (int x = warp; x < n_experts; x += ROUTE_THREADS / 32) {
         const float* w = router + (size_t)x * width;
+        // eight loads of each operand ahead of their eight additions, which keep the order of i
         float acc = 0.f;
-        for (int i = lane; i < width; i += 32) acc = fmaf(Elem<TH>::load(hr + i), w[i], acc);
+        for (int i0 = lane; i0 < width; i0 += 32 * 8) {
+            float hv[8], wv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + 32 * u;
+                hv[u] = i < width ? Elem<TH>::load(hr + i) : 0.f;
+                wv[u] = i < width ? w[i] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc = fmaf(hv[u], wv[u], acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) score[x] = acc;
     }
