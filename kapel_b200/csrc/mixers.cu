@@ -7,8 +7,8 @@
 //                    The counterpart of rotate-and-append for a mixer without a rotation.
 //  head_gate         y[r, h, :] (optionally divided by its root mean square over the head, times a
 //                    weight over all heads) times sigmoid(gate[r, h, :]), the gate read from the
-//                    stacked product.
-//  entry_ranges      first row and row count of every request of a step, from the rows' entries.
+//                    stacked product; the output's rows may be wider than the heads (zeros behind them).
+//  entry_ranges      first row and one past the last row of every request of a step, from the rows' entries.
 //
 // Sums, norms and the sigmoid are 32-bit.
 #include "common.cuh"
@@ -70,7 +70,8 @@ __global__ void proj_norm_append_kernel(const Src<TS> src, int row_width, int q_
 // One warp a (row, head).
 template <typename TY, typename TS, typename TW, typename TO>
 __global__ void head_gate_kernel(TO* __restrict__ out, const TY* __restrict__ y, const Src<TS> gate, int row_width,
-                                 int g_off, const TW* __restrict__ w, int unit, float eps, long long pairs, int heads, int e) {
+                                 int g_off, const TW* __restrict__ w, int unit, float eps, long long pairs, int heads, int e,
+                                 int out_stride) {
     const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (pair >= pairs) return;
     const int lane = threadIdx.x & 31;
@@ -92,8 +93,11 @@ __global__ void head_gate_kernel(TO* __restrict__ out, const TY* __restrict__ y,
         if (w != nullptr) v *= Elem<TW>::load(w + (size_t)h * e + c);
         const float z = gate.at((size_t)r * row_width + g_off + (size_t)h * e + c);
         v *= 1.f / (1.f + expf(-z));
-        Elem<TO>::store(out + (size_t)pair * e + c, v);
+        Elem<TO>::store(out + (size_t)r * out_stride + (size_t)h * e + c, v);
     }
+    // a row wider than its heads (padding for the product that follows) ends in zeros
+    if (h == heads - 1)
+        for (int c = heads * e + lane; c < out_stride; c += 32) Elem<TO>::store(out + (size_t)r * out_stride + c, 0.f);
 }
 
 __global__ void entry_ranges_clear_kernel(int entries, int* __restrict__ start, int* __restrict__ end) {
@@ -166,8 +170,9 @@ extern "C" int kb_proj_norm_append(const void* src, int in_dt, int splits, long 
 
 extern "C" int kb_head_gate(void* out, int out_dt, const void* y, int y_dt, const void* gate, int g_dt, int splits,
                             long long split_stride, int row_width, int g_off, const void* w, int w_dt, int unit, float eps,
-                            long long rows, int heads, int e, void* stream) {
+                            long long rows, int heads, int e, int out_stride, void* stream) {
     KB_REQUIRE(rows >= 0 && heads > 0 && e > 0, "head_gate: rows %lld, heads %d of %d", rows, heads, e);
+    KB_REQUIRE(out_stride >= heads * e, "head_gate: output rows of %d values for %d heads of %d", out_stride, heads, e);
     KB_REQUIRE(row_width > 0 && g_off >= 0 && g_off + heads * e <= row_width, "head_gate: gate columns %d.. do not fit a row of %d", g_off, row_width);
     KB_REQUIRE(splits >= 1 && (splits == 1 || split_stride >= rows * row_width), "head_gate: %d slices %lld apart", splits, split_stride);
     if (rows == 0) return 0;
@@ -179,7 +184,7 @@ extern "C" int kb_head_gate(void* out, int out_dt, const void* y, int y_dt, cons
 #define KB_HG(TY, TS, TW, TO)                                                                                       \
     head_gate_kernel<TY, TS, TW, TO><<<(unsigned)blocks, warps * 32, 0, s>>>((TO*)out, (const TY*)y,                    \
                                                                              Src<TS>{(const TS*)gate, splits, (size_t)split_stride}, \
-                                                                             row_width, g_off, (const TW*)w, unit, eps, pairs, heads, e)
+                                                                             row_width, g_off, (const TW*)w, unit, eps, pairs, heads, e, out_stride)
     const int code = y_dt * 8 + g_dt * 4 + w_dt * 2 + out_dt;
     switch (code) {
         case 0: KB_HG(float, float, float, float); break;

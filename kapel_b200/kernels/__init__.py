@@ -703,9 +703,10 @@ def proj_norm_append(stacked, q_off: int, k_off: int, v_off: int, q_norm, k_norm
 
 
 def head_gate(y: torch.Tensor, stacked, g_off: int, weight: Optional[torch.Tensor], unit: bool, eps: float,
-              out_dtype: torch.dtype) -> torch.Tensor:
+              out_dtype: torch.dtype, pad_to: int = 0) -> torch.Tensor:
     """y [rows, heads, e] times sigmoid of the columns g_off.. of `stacked`; with `unit` each head is
-    first divided by its root mean square (eps inside the root); `weight` [heads e] multiplies too."""
+    first divided by its root mean square (eps inside the root); `weight` [heads e] multiplies too.
+    The result is [rows, heads e], or [rows, pad_to] with zeros behind the heads."""
     _need(y, "head_gate input")
     rows, heads, e = y.shape
     src, dt, splits, stride, g_rows, width = _stacked(stacked, "head_gate gate")
@@ -713,11 +714,12 @@ def head_gate(y: torch.Tensor, stacked, g_off: int, weight: Optional[torch.Tenso
         raise KernelError(f"head_gate: {rows} rows against a gate of {g_rows}")
     if weight is not None:
         _need(weight, "head_gate weight", shape=(heads * e,))
-    out = _fresh((rows, heads, e), out_dtype, y.device)
+    stride = max(int(pad_to), heads * e)
+    out = _fresh((rows, stride), out_dtype, y.device)
     _check(library().kb_head_gate(
         _ptr(out), _CODES[out_dtype], _ptr(y), _dt(y, "head_gate input"), _ptr(src), dt, splits, ctypes.c_longlong(stride), width,
         int(g_off), _ptr(weight), _dt(weight, "head_gate weight") if weight is not None else F32, int(bool(unit)), _f(eps),
-        ctypes.c_longlong(rows), heads, e, _stream()))
+        ctypes.c_longlong(rows), heads, e, stride, _stream()))
     return out
 
 

@@ -18,7 +18,7 @@ import torch
 
 from .. import kernels as K
 from ..cache import CacheNeeds, PagedKV
-from .base import Part, linear, matrix_named, require_product_widths, stack_rows
+from .base import Part, linear, matrix_named, pad_columns, product_width, require_product_widths, stack_rows
 from .registry import build_part
 
 
@@ -52,8 +52,11 @@ class Attention(Part):
         for n, width in ((spec.q_norm, spec.num_heads * spec.head_dim), (spec.k_norm, spec.num_kv_heads * spec.head_dim)):
             if n is not None and (n.kind != "rms" or n.width != width):
                 raise ValueError(f"attention: a norm over the whole projection must be an RMS norm of width {width}")
-        require_product_widths(ctx, "attention", hidden_size=spec.hidden,
-                               **{"num_attention_heads x value size": spec.num_heads * self.v_dim})
+        if self.general and spec.gated:      # the gate kernel writes the output product's input as wide as that product needs it
+            require_product_widths(ctx, "attention", hidden_size=spec.hidden)
+        else:
+            require_product_widths(ctx, "attention", hidden_size=spec.hidden,
+                                   **{"num_attention_heads x value size": spec.num_heads * self.v_dim})
         self.position = build_part("position", spec.position, ctx)
         if self.general and self.position.rotary_dim:
             raise ValueError("attention: a rotation together with projection norms, a gate, kept first keys or another value size is not built")
@@ -63,6 +66,8 @@ class Attention(Part):
         names = [w["q"], w["k"], w["v"]] + ([w["g"]] if self.spec.gated else [])
         self.w_qkv = stack_rows(self.ctx, tensors, names, "attention")
         self.w_o = matrix_named(self.ctx, tensors, w["o"])
+        if self.general and self.spec.gated:
+            self.w_o = pad_columns(self.ctx, self.w_o)
         self.proj_norms = []
         for n in (self.spec.q_norm, self.spec.k_norm):
             if n is None:
@@ -101,7 +106,9 @@ class Attention(Part):
                 q, k_table, v_table, group.block_table, batch.row_entry, batch.row_count, self.ctx.page_size, s.window, s.scale,
                 s.softcap, batch.attention_slots(s.window, s.keep_first), s.keep_first)
         if s.gated:
-            y = K.head_gate(y, stacked, nq + nk + s.num_kv_heads * dv, None, False, 0.0, self.ctx.dtype)
+            y = K.head_gate(y, stacked, nq + nk + s.num_kv_heads * dv, None, False, 0.0, self.ctx.dtype,
+                            pad_to=product_width(self.ctx, s.num_heads * dv))
+            return linear(self.ctx, y, self.w_o, keep_split=True)
         return linear(self.ctx, y.view(y.shape[0], s.num_heads * dv), self.w_o, keep_split=True)
 
     def forward(self, h, batch, cache):

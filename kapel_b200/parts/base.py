@@ -151,6 +151,23 @@ def stack_rows(ctx: BuildContext, tensors, names, what: str = "weights") -> torc
     return stacked
 
 
+def product_width(ctx: BuildContext, k: int) -> int:
+    """The inner width a product of `k` values runs at: on the bfloat16 path the next multiple of 8
+    (rows are read 16 bytes at a time), on the 32-bit path `k` itself."""
+    return k if ctx.is_f32 else -(-k // 8) * 8
+
+
+def pad_columns(ctx: BuildContext, w: torch.Tensor) -> torch.Tensor:
+    """A weight [n, k] with zero columns up to `product_width(k)`: a part whose own kernel writes the
+    product's input may write it that wide (zeros behind), and then any k is taken."""
+    k8 = product_width(ctx, w.shape[1])
+    if k8 == w.shape[1]:
+        return w
+    out = torch.zeros((w.shape[0], k8), dtype=w.dtype, device=w.device)
+    out[:, : w.shape[1]] = w
+    return out
+
+
 def require_product_widths(ctx: BuildContext, what: str, **widths) -> None:
     """Refuses, when a part is built, inner widths that the bfloat16 products cannot take (their
     rows are read 16 bytes at a time: a multiple of 8 elements), naming the configuration's key.

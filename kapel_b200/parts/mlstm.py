@@ -14,7 +14,7 @@ import torch
 
 from .. import kernels as K
 from ..cache import CacheNeeds, StateSpec
-from .base import Part, linear, matrix_named, require_product_widths, stack_rows
+from .base import Part, linear, matrix_named, pad_columns, product_width, require_product_widths, stack_rows
 
 
 class MLSTM(Part):
@@ -36,12 +36,12 @@ class MLSTM(Part):
             raise ValueError(f"mlstm: a key size of {spec.head_dim} is more than the scan kernel's 256")
         if spec.gate_cap <= 0:
             raise ValueError(f"mlstm: gate cap {spec.gate_cap} must be positive")
-        require_product_widths(ctx, "mlstm", hidden_size=spec.hidden, **{"heads x value size": spec.num_heads * spec.v_head_dim})
+        require_product_widths(ctx, "mlstm", width=spec.hidden)
 
     def load(self, tensors):
         w = self.spec.weights
         self.w_in = stack_rows(self.ctx, tensors, [w["q"], w["k"], w["v"], w["g"], w["i"], w["f"]], "mlstm")
-        self.w_o = matrix_named(self.ctx, tensors, w["o"])
+        self.w_o = pad_columns(self.ctx, matrix_named(self.ctx, tensors, w["o"]))      # the gate kernel writes rows this wide
         dev = self.ctx.device
         self.bias_i = tensors[w["i_bias"]].to(dev).float().contiguous()
         self.bias_f = tensors[w["f_bias"]].to(dev).float().contiguous()
@@ -59,5 +59,5 @@ class MLSTM(Part):
         o = K.mlstm_scan(stacked, 0, hd, 2 * hd, 2 * hd + 2 * he, 2 * hd + 2 * he + s.num_heads, self.bias_i, self.bias_f,
                          cache.state(), batch.entry_ranges(), batch.slots, batch.entries, s.num_heads, s.head_dim, s.v_head_dim,
                          s.gate_cap, s.head_dim ** -0.5, s.floor)
-        y = K.head_gate(o, stacked, 2 * hd + he, self.norm_weight, True, s.eps, self.ctx.dtype)
-        return linear(self.ctx, y.view(y.shape[0], he), self.w_o, keep_split=True)
+        y = K.head_gate(o, stacked, 2 * hd + he, self.norm_weight, True, s.eps, self.ctx.dtype, pad_to=product_width(self.ctx, he))
+        return linear(self.ctx, y, self.w_o, keep_split=True)

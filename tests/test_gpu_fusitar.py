@@ -33,12 +33,12 @@ def moe(experts, top, count, keep, ff):
 FUSITAR_A = {"architecture": "Fusitar", "vocab": 211, "width": 64, "embedding": {"scale": 6.5}, "norm": {"eps": 1e-6}, "layers": [
     attention_layer(4, 2, 16, 24, 0.21, 20, 3, moe(8, 3, 4, 2, 40)),
     mlstm_layer(2, 24, 16, 8.0, moe(8, 3, 4, 2, 40)),
-    attention_layer(2, 2, 8, 8, 0.4, 7, 0, None),
+    attention_layer(2, 2, 8, 6, 0.4, 7, 0, None),
     mlstm_layer(4, 8, 8, 12.0, moe(4, 2, 2, 2, 20)),
 ]}
 FUSITAR_B = {"architecture": "Fusitar", "vocab": 97, "width": 96, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-5}, "layers": [
     mlstm_layer(3, 16, 32, 15.0, moe(6, 1, 1, 1, 24)),
-    mlstm_layer(1, 40, 24, 5.0, None),
+    mlstm_layer(1, 40, 20, 5.0, None),
     attention_layer(6, 1, 32, 32, 0.125, 33, 5, moe(6, 2, 3, 2, 56)),
 ]}
 CONFIGS = {"A": (FUSITAR_A, 11), "B": (FUSITAR_B, 12)}
@@ -250,6 +250,8 @@ def test_head_gate_against_plain(unit):
     want = (PF.rms_unit(y, 1e-4) if unit else y).reshape(rows, -1) * (w if unit else 1.0) * PF.sigmoid(g[:, 7:])
     got = K.head_gate(dev(y), dev(g), 7, dev(w) if unit else None, unit, 1e-4, torch.float32)
     assert rel_err(got.cpu().numpy().reshape(rows, -1), want) < 1e-5
+    wide = K.head_gate(dev(y), dev(g), 7, dev(w) if unit else None, unit, 1e-4, torch.float32, pad_to=64).cpu().numpy()
+    assert wide.shape == (rows, 64) and np.array_equal(wide[:, :60], got.cpu().numpy().reshape(rows, -1)) and not wide[:, 60:].any()
 
 
 @pytest.mark.parametrize("heads,d,e,cap", [(2, 24, 16, 8.0), (3, 9, 33, 15.0), (1, 130, 20, 2.0)])
