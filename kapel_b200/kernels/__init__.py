@@ -714,12 +714,12 @@ def head_gate(y: torch.Tensor, stacked, g_off: int, weight: Optional[torch.Tenso
         raise KernelError(f"head_gate: {rows} rows against a gate of {g_rows}")
     if weight is not None:
         _need(weight, "head_gate weight", shape=(heads * e,))
-    stride = max(int(pad_to), heads * e)
-    out = _fresh((rows, stride), out_dtype, y.device)
+    out_width = max(int(pad_to), heads * e)
+    out = _fresh((rows, out_width), out_dtype, y.device)
     _check(library().kb_head_gate(
         _ptr(out), _CODES[out_dtype], _ptr(y), _dt(y, "head_gate input"), _ptr(src), dt, splits, ctypes.c_longlong(stride), width,
         int(g_off), _ptr(weight), _dt(weight, "head_gate weight") if weight is not None else F32, int(bool(unit)), _f(eps),
-        ctypes.c_longlong(rows), heads, e, stride, _stream()))
+        ctypes.c_longlong(rows), heads, e, out_width, _stream()))
     return out
 
 

@@ -252,6 +252,11 @@ def test_head_gate_against_plain(unit):
     assert rel_err(got.cpu().numpy().reshape(rows, -1), want) < 1e-5
     wide = K.head_gate(dev(y), dev(g), 7, dev(w) if unit else None, unit, 1e-4, torch.float32, pad_to=64).cpu().numpy()
     assert wide.shape == (rows, 64) and np.array_equal(wide[:, :60], got.cpu().numpy().reshape(rows, -1)) and not wide[:, 60:].any()
+    # the gate as split-K partial sums (what a product of a few rows leaves): three slices that add up to it
+    parts = rng.standard_normal((3, rows, g.shape[1]))
+    parts[2] = g - parts[0] - parts[1]
+    split = K.head_gate(dev(y), K.SplitSum(dev(parts)), 7, dev(w) if unit else None, unit, 1e-4, torch.float32)
+    assert rel_err(split.cpu().numpy().reshape(rows, -1), want) < 1e-5
 
 
 @pytest.mark.parametrize("heads,d,e,cap", [(2, 24, 16, 8.0), (3, 9, 33, 15.0), (1, 130, 20, 2.0)])
