@@ -175,7 +175,11 @@ def test_attention_with_kept_first_keys_against_plain(dtype, hq, hkv, d, dv, siz
     for a, b in ((0, 333), (333, T)):
         pos = np.arange(a, b)
         lines = dev(pages[pos // page] * page + pos % page, torch.int32)
-        qq = K.proj_norm_append(stacked[a:b].contiguous(), 0, hq * d, hq * d + hkv * d, (dev(wq, dtype), eps, 0.0), (dev(wk, dtype), eps, 0.0),
+        part = stacked[a:b].contiguous()
+        if a:                                                # the second portion comes as split-K partial sums: two slices that add up to it
+            noise = torch.randn_like(part)
+            part = K.SplitSum(torch.stack([noise, part - noise]).contiguous())
+        qq = K.proj_norm_append(part, 0, hq * d, hq * d + hkv * d, (dev(wq, dtype), eps, 0.0), (dev(wk, dtype), eps, 0.0),
                                 lines, k_table, v_table, hq, hkv, d, dv, True, dtype)
         slots = min(-(-b // K.attention_chunk()), (size - 1) // K.attention_chunk() + 2) + K.attention_keep_slots(size, keep)
         y = K.paged_attention_rows(qq, k_table, v_table, table, dev(np.zeros(b - a), torch.int32), dev(pos + 1, torch.int32),
@@ -286,7 +290,11 @@ def test_mlstm_scan_in_portions_and_token_by_token_against_plain(heads, d, e, ca
         rows = np.concatenate([data[n][a:b] for n, _, a, b in step])
         entry = np.concatenate([np.full(b - a, i) for i, (_, _, a, b) in enumerate(step)])
         ranges = K.entry_ranges(dev(entry, torch.int32), len(step))
-        out = K.mlstm_scan(dev(rows), 0, heads * d, 2 * heads * d, width - 2 * heads, width - heads, dev(bi), dev(bf), state, ranges,
+        rows = dev(rows)
+        if len(rows) <= 4:                                   # a few rows come as split-K partial sums, as a small product leaves them
+            noise = torch.randn_like(rows)
+            rows = K.SplitSum(torch.stack([noise, rows - noise - 1.0, torch.ones_like(rows)]).contiguous())
+        out = K.mlstm_scan(rows, 0, heads * d, 2 * heads * d, width - 2 * heads, width - heads, dev(bi), dev(bf), state, ranges,
                            dev([s for _, s, _, _ in step], torch.int32), len(step), heads, d, e, cap, d ** -0.5, 1e-6).cpu().numpy()
         at = 0
         for n, _, a, b in step:
