@@ -461,6 +461,39 @@ def test_recorded_passes_leave_the_state_as_eager_ones_do(models):
         assert rel_err(outs[1][step], outs[0][step]) < 2e-6, f"step {step}"
 
 
+ONE_KIND = {
+    "recurrent": {"architecture": "Fusitar", "vocab": 60, "width": 32, "embedding": {"scale": 4.0}, "norm": {"eps": 1e-6}, "layers": [
+        mlstm_layer(2, 8, 12, 6.0, moe(4, 2, 1, 1, 16)), mlstm_layer(1, 24, 8, 10.0, None)]},
+    "attending": {"architecture": "Fusitar", "vocab": 60, "width": 32, "embedding": {"scale": 4.0}, "norm": {"eps": 1e-6}, "layers": [
+        attention_layer(2, 1, 16, 16, 0.25, 12, 2, moe(4, 2, 2, 1, 16)), attention_layer(4, 4, 8, 4, 0.3, 100, 0, None)]},
+}
+
+
+@pytest.mark.parametrize("kind", sorted(ONE_KIND))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_models_of_one_kind_of_mixer(kind, dtype, tmp_path):
+    """No paged group at all, or no state at all (then a prompt alone in its pass is recorded at a rounded
+    length, with rows that are no token's): prompts of one length three times over, then token by token."""
+    from kapel_b200.engine import Engine
+
+    raw = ONE_KIND[kind]
+    folder = make_folder(raw, 5, tmp_path)
+    if dtype == "bfloat16":
+        make_routers_decisive(folder)
+    t = read_tensors(folder)
+    eng = Engine.from_dir(folder, dtype=dtype, max_tokens=512, max_sequences=4)
+    assert (len(eng.cache.groups) == 0) == (kind == "recurrent") and (len(eng.cache.states) == 0) == (kind == "attending")
+    tb, want = TraceBuilder(), {}
+    for n, k in enumerate("xyz"):
+        tokens = random_tokens(np.random.default_rng(n), 83, raw["vocab"])
+        want[k] = PF.forward(raw, t, tokens)
+        tb.step([(k, tokens[:70], [69])])
+        for i in range(70, 83):
+            tb.step([(k, tokens[i : i + 1], [0])], end=([k] if i == 82 else []))
+    compare_trace(run_trace_engine(eng, tb.steps), tb, want, TOL[dtype], f"{kind} {dtype}")
+    assert eng.recorded_passes > 0
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_generation_through_the_entry_point_and_scheduler(models, name):
     """`Model.generate` and `generate_batch` (prompt portions under a token budget, decoding passes
