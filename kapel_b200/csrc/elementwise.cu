@@ -439,6 +439,25 @@ extern "C" int kb_glu(void* out, int out_dt, const void* x, int in_dt, int split
     return check_launch("glu");
 }
 
+// out [rows, wide] = in [rows, width] with zeros behind each row (wide >= width): the input of a product whose
+// weight was given zero columns up to a width its kernel takes.
+__global__ void pad_cols_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ in, long long rows, int width, int wide) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * wide) return;
+    const long long r = i / wide;
+    const int c = (int)(i - r * wide);
+    out[i] = c < width ? in[r * width + c] : __float2bfloat16_rn(0.f);
+}
+
+extern "C" int kb_pad_cols_bf16(void* out, const void* in, long long rows, int width, int wide, void* stream) {
+    KB_REQUIRE(rows >= 0 && width > 0 && wide >= width, "pad_cols: rows %lld, width %d to %d", rows, width, wide);
+    if (rows == 0) return 0;
+    const long long blocks = (rows * wide + 255) / 256;
+    KB_REQUIRE(blocks <= 0x7fffffffll, "pad_cols: too many values for one launch");
+    pad_cols_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((bf16*)out, (const bf16*)in, rows, width, wide);
+    return check_launch("pad_cols");
+}
+
 extern "C" int kb_cast(void* out, int out_dt, const void* in, int in_dt, long long n, void* stream) {
     KB_REQUIRE(n >= 0, "cast: %lld elements", n);
     if (n == 0) return 0;

@@ -320,6 +320,15 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
+def pad_cols(x: torch.Tensor, wide: int) -> torch.Tensor:
+    """x [rows, width] (bfloat16) with zero columns up to `wide`."""
+    _need(x, "pad_cols input", torch.bfloat16)
+    rows, width = x.shape
+    out = _fresh((rows, int(wide)), torch.bfloat16, x.device)
+    _check(library().kb_pad_cols_bf16(_ptr(out), _ptr(x), ctypes.c_longlong(rows), int(width), int(wide), _stream()))
+    return out
+
+
 def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     _need(x, "gather_rows input", torch.float32)
     _need(rows, "gather_rows rows", torch.int32)

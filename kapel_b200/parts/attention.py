@@ -52,9 +52,7 @@ class Attention(Part):
         for n, width in ((spec.q_norm, spec.num_heads * spec.head_dim), (spec.k_norm, spec.num_kv_heads * spec.head_dim)):
             if n is not None and (n.kind != "rms" or n.width != width):
                 raise ValueError(f"attention: a norm over the whole projection must be an RMS norm of width {width}")
-        if self.general and spec.gated:      # the gate kernel writes the output product's input as wide as that product needs it
-            require_product_widths(ctx, "attention", hidden_size=spec.hidden)
-        else:
+        if not self.general:
             require_product_widths(ctx, "attention", hidden_size=spec.hidden,
                                    **{"num_attention_heads x value size": spec.num_heads * self.v_dim})
         self.position = build_part("position", spec.position, ctx)

@@ -183,7 +183,9 @@ def require_product_widths(ctx: BuildContext, what: str, **widths) -> None:
 def linear(ctx: BuildContext, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            softcap: Optional[float] = None, keep_split: bool = False):
     """x . w^T through the library's kernels. A weight kept in 32-bit on the bfloat16 path is
-    multiplied in true 32-bit: the input is widened first and the result narrowed after. With
+    multiplied in true 32-bit: the input is widened first and the result narrowed after. A
+    bfloat16 weight whose inner width is no multiple of 8 is multiplied with zero columns added to
+    it and to the input (a weight already that wide, `pad_columns`, takes a narrower input likewise). With
     `keep_split` the result may be a `kernels.SplitSum` (partial sums of a product split over K)
     for a consumer that adds them up itself: `add_branch`, `kernels.glu`, `kernels.rope_append`."""
     from .. import kernels as K
@@ -193,4 +195,14 @@ def linear(ctx: BuildContext, x: torch.Tensor, w: torch.Tensor, out_dtype: Optio
         x = K.cast(x, torch.float32)
     elif w.dtype == torch.bfloat16 and x.dtype != torch.bfloat16:
         x = K.cast(x, torch.bfloat16)
+    if w.dtype == torch.bfloat16 and w.shape[1] % 8:
+        # an inner width the bfloat16 kernels do not take: zero columns up to the next multiple of 8,
+        # on the weight once (kept beside it) and on the input each time
+        wide = getattr(w, "_kb_wide", None)
+        if wide is None:
+            wide = pad_columns(ctx, w)
+            w._kb_wide = wide
+        w = wide
+    if x.dtype == torch.bfloat16 and x.shape[1] < w.shape[1]:
+        x = K.pad_cols(x, w.shape[1])
     return K.gemm(x, w, out_dtype=out_dtype, softcap=softcap, keep_split=keep_split)

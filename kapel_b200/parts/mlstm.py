@@ -14,7 +14,7 @@ import torch
 
 from .. import kernels as K
 from ..cache import CacheNeeds, StateSpec
-from .base import Part, linear, matrix_named, pad_columns, product_width, require_product_widths, stack_rows
+from .base import Part, linear, matrix_named, pad_columns, product_width, stack_rows
 
 
 class MLSTM(Part):
@@ -36,7 +36,6 @@ class MLSTM(Part):
             raise ValueError(f"mlstm: a key size of {spec.head_dim} is more than the scan kernel's 256")
         if spec.gate_cap <= 0:
             raise ValueError(f"mlstm: gate cap {spec.gate_cap} must be positive")
-        require_product_widths(ctx, "mlstm", width=spec.hidden)
 
     def load(self, tensors):
         w = self.spec.weights

@@ -494,6 +494,32 @@ def test_models_of_one_kind_of_mixer(kind, dtype, tmp_path):
     assert eng.recorded_passes > 0
 
 
+ODD = {"architecture": "Fusitar", "vocab": 77, "width": 52, "embedding": {"scale": 3.0}, "norm": {"eps": 1e-6}, "layers": [
+    attention_layer(3, 1, 12, 10, 0.3, 19, 1, moe(5, 2, 1, 1, 13)), mlstm_layer(2, 10, 6, 7.0, moe(3, 1, 3, 2, 11)),
+    attention_layer(3, 3, 20, 20, 0.2, 40, 3, None)]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_are_no_multiples_of_eight(dtype, tmp_path):
+    """A width, head sizes, value sizes and expert sizes that fit no 16-byte piece: the bfloat16 products run
+    on zero-padded rows, the other kernels value by value."""
+    from kapel_b200.engine import Engine
+
+    folder = make_folder(ODD, 6, tmp_path)
+    if dtype == "bfloat16":
+        make_routers_decisive(folder)
+    t = read_tensors(folder)
+    eng = Engine.from_dir(folder, dtype=dtype, max_tokens=512, max_sequences=4)
+    tokens = random_tokens(np.random.default_rng(3), 95, ODD["vocab"])
+    want = {"a": PF.forward(ODD, t, tokens)}
+    tb = TraceBuilder()
+    tb.step([("a", tokens[:70], range(70))])
+    tb.step([("a", tokens[70:73], range(3))])
+    for i in range(73, 95):
+        tb.step([("a", tokens[i : i + 1], [0])], end=(["a"] if i == 94 else []))
+    compare_trace(run_trace_engine(eng, tb.steps), tb, want, TOL[dtype], f"odd {dtype}")
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_generation_through_the_entry_point_and_scheduler(models, name):
     """`Model.generate` and `generate_batch` (prompt portions under a token budget, decoding passes
