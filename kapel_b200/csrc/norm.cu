@@ -59,7 +59,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const Src<TB> b
         residual[base + i] = r;
         ss2 += r * r;
     }
-    if (w_next == nullptr) return;
+    if (w_next == nullptr) {
+        // no norm follows: with an output, the sum itself in the output's type (what the next reader takes)
+        if (h != nullptr)
+            for (int i = threadIdx.x; i < width; i += blockDim.x) Elem<TH>::store(h + base + i, residual[base + i]);
+        return;
+    }
     ss2 = block_sum(ss2, scratch);
     const float inv2 = 1.f / sqrtf(ss2 / (float)width + eps_next);
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -106,7 +111,16 @@ __global__ void add_rmsnorm_reg_kernel(float* __restrict__ residual, const Src<T
             ss2 += r[e] * r[e];
         }
     }
-    if (w_next == nullptr) return;
+    if (w_next == nullptr) {
+        if (h != nullptr) {
+#pragma unroll
+            for (int e = 0; e < EPT; ++e) {
+                const int i = threadIdx.x + e * blockDim.x;
+                if (i < width) Elem<TH>::store(h + base + i, r[e]);
+            }
+        }
+        return;
+    }
     ss2 = block_sum(ss2, scratch);
     const float inv2 = 1.f / sqrtf(ss2 / (float)width + eps_next);
 #pragma unroll
@@ -178,7 +192,22 @@ __global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ residual, const __
             *reinterpret_cast<float4*>(residual + base + ci * 8 + 4) = make_float4(r[c][4], r[c][5], r[c][6], r[c][7]);
         }
     }
-    if (w_next == nullptr) return;
+    if (w_next == nullptr) {
+        if (h != nullptr) {
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                const int ci = threadIdx.x + c * blockDim.x;
+                if (ci < chunks) {
+                    uint4 uo;
+                    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&uo);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) po[j] = __floats2bfloat162_rn(r[c][2 * j], r[c][2 * j + 1]);
+                    *reinterpret_cast<uint4*>(h + base + ci * 8) = uo;
+                }
+            }
+        }
+        return;
+    }
     ss2 = block_sum(ss2, scratch);
     const float inv2 = 1.f / sqrtf(ss2 / (float)width + eps_next);
 #pragma unroll
@@ -285,6 +314,20 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
         }
     }
     if (w_next == nullptr) {
+        if (h != nullptr) {
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                const int ci = threadIdx.x + c * blockDim.x;
+                if (ci < chunks) {
+                    uint2 uo;
+                    __nv_bfloat162 o0 = __floats2bfloat162_rn(r[c].x, r[c].y);
+                    __nv_bfloat162 o1 = __floats2bfloat162_rn(r[c].z, r[c].w);
+                    uo.x = *reinterpret_cast<uint32_t*>(&o0);
+                    uo.y = *reinterpret_cast<uint32_t*>(&o1);
+                    *reinterpret_cast<uint2*>(h + base + ci * 4) = uo;
+                }
+            }
+        }
         KB_TL_LEAVE(norm, blockIdx.x == 0, 0);
         return;
     }
@@ -422,6 +465,20 @@ __global__ void add_rmsnorm_splits_bulk_kernel(float* __restrict__ residual, con
     }
     if (!ok && threadIdx.x == 0) atomicExch(&g_norm_error, 1);
     if (w_next == nullptr) {
+        if (h != nullptr) {
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                const int ci = threadIdx.x + c * blockDim.x;
+                if (ci < chunks) {
+                    uint2 uo;
+                    __nv_bfloat162 o0 = __floats2bfloat162_rn(r[c].x, r[c].y);
+                    __nv_bfloat162 o1 = __floats2bfloat162_rn(r[c].z, r[c].w);
+                    uo.x = *reinterpret_cast<uint32_t*>(&o0);
+                    uo.y = *reinterpret_cast<uint32_t*>(&o1);
+                    *reinterpret_cast<uint2*>(h + base + ci * 4) = uo;
+                }
+            }
+        }
         KB_TL_LEAVE(norm, blockIdx.x == 0, 0);
         return;
     }

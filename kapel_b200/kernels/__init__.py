@@ -350,10 +350,11 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float, ou
     return y
 
 
-def add_rmsnorm(residual, branch, post, nxt, out_dtype):
+def add_rmsnorm(residual, branch, post, nxt, out_dtype, copy_out: bool = False):
     """residual += norm_post(branch) (post = (weight, eps, offset) or None: plain add); returns
-    norm_next(residual) when nxt = (weight, eps, offset) is given, else None. In place on
-    residual. `branch` is a tensor or a SplitSum."""
+    norm_next(residual) when nxt = (weight, eps, offset) is given; without it, None, or with
+    `copy_out` the new residual itself in `out_dtype` (what a reader of the residual takes next).
+    In place on residual. `branch` is a tensor or a SplitSum."""
     rows, width = residual.shape
     _need(residual, "add_rmsnorm residual", torch.float32)
     src, b_dt, splits, stride = _src(branch, "add_rmsnorm branch")
@@ -367,7 +368,7 @@ def add_rmsnorm(residual, branch, post, nxt, out_dtype):
     if len({w.dtype for w in ws}) > 1:
         raise KernelError("add_rmsnorm: the two norms' weights differ in dtype; call the norms one by one")
     w_dt = _dt(ws[0], "add_rmsnorm weight") if ws else F32
-    h = _fresh((rows, width), out_dtype, residual.device) if w_next is not None else None
+    h = _fresh((rows, width), out_dtype, residual.device) if (w_next is not None or copy_out) else None
     _check(
         library().kb_add_rmsnorm(_ptr(residual), _ptr(src), b_dt, splits, ctypes.c_longlong(stride), _ptr(w_post), _f(eps_post),
                                  _f(off_post), _ptr(w_next), _f(eps_next), _f(off_next), _ptr(h), _CODES[out_dtype], w_dt,

@@ -126,10 +126,13 @@ class PostNormBlock(Part):
         return x if self.ctx.is_f32 else K.cast(x, self.ctx.dtype)
 
     def forward(self, x, h, batch, cache, next_norm):
-        a = self.mixer.forward(self._read(x), batch, cache)
-        add_branch(self.ctx, x, a, self.norms["post_mixer"], None)
-        if self.ffn is None:
-            return x, (next_norm.forward(x) if next_norm is not None else None)
-        m = self.ffn.forward(self._read(x))
-        h_next = add_branch(self.ctx, x, m, self.norms["post_ffn"], next_norm)
-        return x, h_next
+        """`h`, where given, is the residual already in the activation dtype: the block before left it
+        with its last sum (this block's `first_norm()` is None, so the engine never norms ahead)."""
+        narrow = not self.ctx.is_f32                         # the branches read a rounded copy of the residual
+        a = self.mixer.forward(h if (h is not None and narrow) else self._read(x), batch, cache)
+        last = self.ffn is None
+        h = add_branch(self.ctx, x, a, self.norms["post_mixer"], next_norm if last else None, copy_out=narrow)
+        if last:
+            return x, h
+        m = self.ffn.forward(h if narrow else x)
+        return x, add_branch(self.ctx, x, m, self.norms["post_ffn"], next_norm, copy_out=narrow)

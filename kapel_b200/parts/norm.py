@@ -27,15 +27,16 @@ class RMSNorm(Part):
         return (self.weight, self.spec.eps, self.spec.offset)
 
 
-def add_branch(ctx, residual, branch, post_norm, next_norm):
+def add_branch(ctx, residual, branch, post_norm, next_norm, copy_out: bool = False):
     """residual += post_norm(branch) (post_norm None: plain sum); returns next_norm(residual),
-    or None without a next norm. One kernel when the norms are RMS norms with weights of one
-    dtype; a norm of another kind runs through its own `forward` around the fused sum."""
+    or None without a next norm (with `copy_out`: the new residual in the activation dtype, for a
+    block whose branches read the residual itself). One kernel when the norms are RMS norms with
+    weights of one dtype; a norm of another kind runs through its own `forward` around the fused sum."""
     post_key = post_norm.fuse_key() if hasattr(post_norm, "fuse_key") else None
     next_key = next_norm.fuse_key() if hasattr(next_norm, "fuse_key") else None
     if post_norm is not None and post_key is None:
         branch = post_norm.forward(K.finish(branch, ctx.dtype))
     if next_key is not None and (post_key is None or post_key[0].dtype == next_key[0].dtype):
         return K.add_rmsnorm(residual, branch, post_key, next_key, ctx.dtype)
-    K.add_rmsnorm(residual, branch, post_key, None, ctx.dtype)
-    return next_norm.forward(residual) if next_norm is not None else None
+    copied = K.add_rmsnorm(residual, branch, post_key, None, ctx.dtype, copy_out=copy_out and next_norm is None)
+    return next_norm.forward(residual) if next_norm is not None else copied
