@@ -253,7 +253,8 @@ moe_grouped_f32_kernel(const GroupedParams p) {
 // columns with WM x WN warps; tiles of TK k values arrive by 16-byte asynchronous copies, three
 // stages deep, so that a block that walks one expert's weights for a handful of rows (a decoding
 // step) keeps loads in flight instead of waiting for each tile; rows of k that are no multiple of
-// 8 are loaded value by value. Two shapes: 32 x 64 (few rows an expert) and 64 x 128 (prompts).
+// 8 are loaded value by value. Two shapes: 32 x 64 (few rows an expert) and 64 x 128 (prompts); 128 x 128 was
+// built and measured no faster (the products run at about 215 TFLOP/s either way).
 constexpr int BSTAGES = 3;
 
 __device__ __forceinline__ void moe_copy16(void* dst, const void* src, bool valid) {
@@ -262,16 +263,24 @@ __device__ __forceinline__ void moe_copy16(void* dst, const void* src, bool vali
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d32), "l"(src), "r"(bytes) : "memory");
 }
 
+__device__ __forceinline__ void moe_ldmatrix4(uint32_t (&r)[4], const void* at) {
+    const uint32_t a32 = (uint32_t)__cvta_generic_to_shared(at);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a32));
+}
+
 template <typename TO, int TM, int TN, int WM, int WN, int TK>
 __global__ void __launch_bounds__(WM * WN * 32)
 moe_grouped_bf16_kernel(const GroupedParams p) {
+    static_assert((TN / WN / 8) % 2 == 0, "a warp's n8 tiles come in pairs");
     constexpr int THREADS = WM * WN * 32;
     constexpr int MT = TM / WM / 16, NT = TN / WN / 8;       // m16 and n8 tiles a warp
     const int tile = blockIdx.x;
     if (tile >= p.n_tiles[0]) return;
-    __shared__ __align__(16) bf16 As[BSTAGES][TM][TK + 8];
-    __shared__ __align__(16) bf16 Ws[BSTAGES][TN][TK + 8];
-    __shared__ int arow[TM], orow[TM];
+    extern __shared__ __align__(16) unsigned char moe_smem[];      // As [stages][TM][TK + 8] | Ws [stages][TN][TK + 8] | arow | orow
+    bf16 (*As)[TM][TK + 8] = reinterpret_cast<bf16 (*)[TM][TK + 8]>(moe_smem);
+    bf16 (*Ws)[TN][TK + 8] = reinterpret_cast<bf16 (*)[TN][TK + 8]>(moe_smem + sizeof(bf16) * BSTAGES * TM * (TK + 8));
+    int* arow = reinterpret_cast<int*>(moe_smem + sizeof(bf16) * BSTAGES * (TM + TN) * (TK + 8));
+    int* orow = arow + TM;
     const int expert = p.tile_expert[tile], first = p.tile_first[tile], nrows = p.tile_rows[tile];
     const int n0 = blockIdx.y * TN;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -326,20 +335,17 @@ moe_grouped_bf16_kernel(const GroupedParams p) {
         const int st = kt % BSTAGES;
 #pragma unroll
         for (int ks = 0; ks < TK; ks += 16) {
+            // four 8 x 8 pieces an instruction: an m16 x k16 piece of A, or the k16 pieces of two n8 tiles of W
             uint32_t af[MT][4], bfr[NT][2];
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const int r0 = wm * (TM / WM) + mt * 16 + grp;
-                af[mt][0] = *reinterpret_cast<const uint32_t*>(&As[st][r0][ks + qd * 2]);
-                af[mt][1] = *reinterpret_cast<const uint32_t*>(&As[st][r0 + 8][ks + qd * 2]);
-                af[mt][2] = *reinterpret_cast<const uint32_t*>(&As[st][r0][ks + qd * 2 + 8]);
-                af[mt][3] = *reinterpret_cast<const uint32_t*>(&As[st][r0 + 8][ks + qd * 2 + 8]);
-            }
+            for (int mt = 0; mt < MT; ++mt)
+                moe_ldmatrix4(af[mt], &As[st][wm * (TM / WM) + mt * 16 + (lane & 15)][ks + (lane >> 4) * 8]);
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const int c0 = wn * (TN / WN) + nt * 8 + grp;
-                bfr[nt][0] = *reinterpret_cast<const uint32_t*>(&Ws[st][c0][ks + qd * 2]);
-                bfr[nt][1] = *reinterpret_cast<const uint32_t*>(&Ws[st][c0][ks + qd * 2 + 8]);
+            for (int np = 0; np < NT / 2; ++np) {
+                uint32_t b4[4];
+                moe_ldmatrix4(b4, &Ws[st][wn * (TN / WN) + np * 16 + (lane & 7) + ((lane >> 4) << 3)][ks + ((lane >> 3) & 1) * 8]);
+                bfr[2 * np][0] = b4[0]; bfr[2 * np][1] = b4[1];
+                bfr[2 * np + 1][0] = b4[2]; bfr[2 * np + 1][1] = b4[3];
             }
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
@@ -431,7 +437,7 @@ extern "C" int kb_moe_grouped(void* out, int out_dt, const void* a, const void* 
     GroupedParams p;
     p.a = a; p.w = w; p.out = out; p.order = order; p.tile_expert = tile_expert; p.tile_first = tile_first; p.tile_rows = tile_rows;
     p.n_tiles = n_tiles; p.n = n; p.k = k; p.top = top; p.act = act; p.a_by = a_by_token; p.out_by = out_by_pair;
-    const int tn = rows_a_tile == GM_LARGE ? 128 : GN;
+    const int tn = rows_a_tile == GM ? GN : 128;
     const int col_tiles = (n + tn - 1) / tn;
     KB_REQUIRE(col_tiles <= 65535, "moe_grouped: %d columns are too many for one launch", n);
     dim3 grid(tile_cap, col_tiles);
@@ -441,13 +447,28 @@ extern "C" int kb_moe_grouped(void* out, int out_dt, const void* a, const void* 
         moe_grouped_f32_kernel<<<grid, GEMM_THREADS, 0, s>>>(p);
     } else if (dt == KB_DT_BF16) {
         KB_REQUIRE(out_dt == KB_DT_F32 || out_dt == KB_DT_BF16, "moe_grouped: output dtype code %d is not known", out_dt);
+#define KB_MOE_TILE(TO, TM, TN, WM, WN, TK)                                                                                \
+    do {                                                                                                                   \
+        constexpr size_t bytes = sizeof(bf16) * BSTAGES * (TM + TN) * (TK + 8) + 2 * TM * sizeof(int);                     \
+        if (bytes > 48 * 1024) {                                                                                           \
+            static bool set = false;                                                                                       \
+            if (!set) {                                                                                                    \
+                if (cudaFuncSetAttribute(moe_grouped_bf16_kernel<TO, TM, TN, WM, WN, TK>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)bytes) != cudaSuccess)                                                       \
+                    return fail("moe_grouped: cannot have %zu bytes of shared memory", bytes);                             \
+                set = true;                                                                                                \
+            }                                                                                                              \
+        }                                                                                                                  \
+        moe_grouped_bf16_kernel<TO, TM, TN, WM, WN, TK><<<grid, WM * WN * 32, bytes, s>>>(p);                                \
+    } while (0)
         if (rows_a_tile == GM_LARGE) {
-            if (out_dt == KB_DT_F32) moe_grouped_bf16_kernel<float, GM_LARGE, 128, 2, 4, 32><<<grid, 256, 0, s>>>(p);
-            else moe_grouped_bf16_kernel<bf16, GM_LARGE, 128, 2, 4, 32><<<grid, 256, 0, s>>>(p);
+            if (out_dt == KB_DT_F32) KB_MOE_TILE(float, GM_LARGE, 128, 2, 4, 32);
+            else KB_MOE_TILE(bf16, GM_LARGE, 128, 2, 4, 32);
         } else {
-            if (out_dt == KB_DT_F32) moe_grouped_bf16_kernel<float, GM, GN, 1, 4, 64><<<grid, 128, 0, s>>>(p);
-            else moe_grouped_bf16_kernel<bf16, GM, GN, 1, 4, 64><<<grid, 128, 0, s>>>(p);
+            if (out_dt == KB_DT_F32) KB_MOE_TILE(float, GM, GN, 1, 4, 64);
+            else KB_MOE_TILE(bf16, GM, GN, 1, 4, 64);
         }
+#undef KB_MOE_TILE
     } else return fail("moe_grouped: dtype code %d is not known", dt);
     return check_launch("moe_grouped");
 }

@@ -349,7 +349,7 @@ def test_router_against_plain(experts, top, count, keep):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("rows,width,ff,experts,top", [(70, 40, 24, 6, 2), (1, 64, 100, 5, 5), (200, 24, 9, 3, 1), (700, 72, 136, 4, 2)])
+@pytest.mark.parametrize("rows,width,ff,experts,top", [(70, 40, 24, 6, 2), (1, 64, 100, 5, 5), (200, 24, 9, 3, 1), (700, 72, 136, 4, 2), (900, 40, 130, 3, 1)])
 def test_experts_against_plain(dtype, tol, rows, width, ff, experts, top):
     from kapel_b200 import kernels as K
 
