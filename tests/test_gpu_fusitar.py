@@ -549,3 +549,36 @@ def test_greedy_generation_through_the_entry_point_and_scheduler(models, name):
         safe = next((i for i, m in enumerate(margins) if m < 1e-3), len(margins))
         assert got[:safe] == tokens[:safe]
     assert model.engine.cache.free_pages() == model.engine.cache.total_pages()
+
+
+def test_replay_program_and_command_line(models, tmp_path):
+    """`bin/trace_run` and `python -m kapel_b200 run` take a Fusitar folder as they take any other: the
+    program's logits are the plain ones, the command's greedy tokens are the entry point's."""
+    import subprocess
+    import sys
+
+    import kapel_b200
+    from helpers import ROOT
+
+    folder, raw, _ = models["A"]
+    tokens = random_tokens(np.random.default_rng(4), 40, raw["vocab"])
+    want = plain(models, "A", tokens)
+    steps = [{"step": 0, "entries": [{"id": "q", "tokens": tokens[:33], "want": [0, 32]}], "end": []},
+             {"step": 1, "entries": [{"id": "q", "tokens": tokens[33:35], "want": []}], "end": []},
+             {"step": 5, "entries": [{"id": "q", "tokens": tokens[35:], "want": [4]}], "end": ["q"]}]
+    out = tmp_path / "logits"
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "64"], input="".join(json.dumps(x) + "\n" for x in steps), capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr
+    assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == ["done 0", "done 1", "done 5"]
+    assert sorted(f.name for f in out.iterdir()) == ["0.f32", "5.f32"]
+    first = np.fromfile(out / "0.f32", dtype="<f4").reshape(2, raw["vocab"])
+    last = np.fromfile(out / "5.f32", dtype="<f4").reshape(1, raw["vocab"])
+    assert rel_err(first, want[[0, 32]]) < TOL["float32"] and rel_err(last, want[[39]]) < TOL["float32"]
+
+    model = kapel_b200.Model(str(folder), dtype="f32", max_tokens_cached=256, max_sequences=2)
+    expect = model.generate(tokens[:9], max_tokens=6)
+    r = subprocess.run([sys.executable, "-m", "kapel_b200", "run", str(folder), "--tokens", ",".join(map(str, tokens[:9])), "--max-tokens", "6",
+                        "--greedy", "--dtype", "f32"], capture_output=True, text=True, timeout=900, cwd=str(ROOT))
+    assert r.returncode == 0, r.stderr
+    assert [int(x) for x in r.stdout.strip().splitlines()[0].split(",")] == expect
