@@ -33,13 +33,16 @@ from .pages import CacheFull, host_library
 @dataclass(frozen=True)
 class PagedKV:
     """Keys of `kv_heads` heads of `head_dim` and values of `v_head_dim` (None: the keys' size);
-    `window` None keeps every key, else the last `window` positions and the first `keep_first`."""
+    `window` None keeps every key, else the last `window` positions and the first `keep_first`.
+    With `shared_values` a layer has one table: its values are read out of its keys' lines (a
+    latent that is both), and `tables(layer)` gives that table twice."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     keep_first: int = 0
     v_head_dim: Optional[int] = None
+    shared_values: bool = False
 
 
 @dataclass(frozen=True)
@@ -108,6 +111,8 @@ class CacheGroup:
     def name(self) -> str:
         w = "all" if self.window is None else f"window{self.window}" + (f"+first{self.keep_first}" if self.keep_first else "")
         v = "" if self.needs.v_head_dim in (None, self.needs.head_dim) else f"/v{self.needs.v_head_dim}"
+        if self.needs.shared_values:
+            v = "/v=k"
         return f"{w}/h{self.needs.kv_heads}/d{self.needs.head_dim}{v}"
 
 
@@ -191,7 +196,7 @@ class CacheManager:
             v_shape = (*shape[:3], g.needs.v_head_dim or g.needs.head_dim)
             for layer in g.layers:
                 g.keys[layer] = allocate(shape, dtype)
-                g.values[layer] = allocate(v_shape, dtype)
+                g.values[layer] = g.keys[layer] if g.needs.shared_values else allocate(v_shape, dtype)
         for layer, spec in self.state_specs.items():
             self.states[layer] = allocate((self.max_sequences + 1, *spec.shape), spec.dtype)
 

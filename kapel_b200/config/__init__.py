@@ -1,6 +1,7 @@
 """Typed configurations, the model-as-data records, and the architecture registry."""
 from .fusitar import FusitarConfig
 from .gemma2 import ConfigError, Gemma2Config
+from .kofutar import KofutarConfig
 from .registry import (
     architectures,
     config_class_for,
@@ -14,9 +15,12 @@ from .registry import (
 from .spec import (
     AttentionSpec,
     BlockSpec,
+    DeltaSpec,
     EmbedSpec,
     GatedMLPSpec,
     HeadSpec,
+    InputMixSpec,
+    LatentAttentionSpec,
     MLSTMSpec,
     ModelSpec,
     MoESpec,

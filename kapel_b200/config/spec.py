@@ -16,7 +16,8 @@ from typing import Mapping, Optional, Tuple
 
 @dataclass(frozen=True)
 class NormSpec:
-    """y = x / sqrt(mean(x^2) + eps) * (offset + w) for kind "rms"."""
+    """y = x / sqrt(mean(x^2) + eps) * (offset + w) for kind "rms"; kind "layer" takes the row's mean
+    off first: y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * (offset + w), without a bias."""
 
     width: int
     eps: float
@@ -27,12 +28,14 @@ class NormSpec:
 
 @dataclass(frozen=True)
 class PositionSpec:
-    """kind "rope": rotation of the first `rotary_dim` components, pairing "half" (j, j+r/2)."""
+    """kind "rope": rotation of the first `rotary_dim` components, pairing "half" (j, j+r/2), by the
+    angle position * theta^(-2j/r) / `divisor` (a divisor above 1 stretches the positions)."""
 
     kind: str = "rope"
     theta: float = 10000.0
     rotary_dim: int = 0
     pairing: str = "half"
+    divisor: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -45,6 +48,8 @@ class AttentionSpec:
     names, each [out, in]; with `gated`, role g as well: the heads' outputs are multiplied by
     sigmoid(g(h)) ahead of o. `v_head_dim` None: values have the keys' size. `q_norm` / `k_norm`:
     a norm over the whole projection (all heads' rows at once) ahead of the split into heads.
+    `q_head_norm` / `k_head_norm`: an RMS norm over each head's vector with one weight of the head's
+    size for all heads, ahead of the rotation.
     """
 
     hidden: int
@@ -62,6 +67,62 @@ class AttentionSpec:
     q_norm: Optional[NormSpec] = None
     k_norm: Optional[NormSpec] = None
     gated: bool = False
+    q_head_norm: Optional[NormSpec] = None
+    k_head_norm: Optional[NormSpec] = None
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose queries and whose keys and values come through low-rank latents.
+
+    c_q = rms(dq h) [q_rank]; every head's query is uq c_q: `head_dim` plain components, then
+    `rot_dim` rotated ones. dkv h gives the latent c [kv_rank] (RMS-normed) and, behind it, one
+    rotated key part [rot_dim] shared by all heads (not normed). A head's plain key is uk c, its
+    value uv c; score = (q_plain . k_plain + q_rot . k_rot) * `scale`. Only c and the rotated part
+    are kept in the cache. With `sink`, e^(sink[head]) joins the softmax's denominator; with
+    `gated`, the heads' outputs are multiplied by sigmoid(g(h)) ahead of o. `weights`: dq, dq_norm,
+    uq, dkv, dkv_norm, uk, uv, o, and sink, g where used.
+    """
+
+    hidden: int
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    v_head_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    eps: float
+    position: PositionSpec
+    weights: Mapping[str, str]
+    sink: bool = False
+    gated: bool = False
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class DeltaSpec:
+    """The gated delta rule: a matrix memory S [head_dim, v_head_dim] a head and request.
+
+    q, k [kv_heads, head_dim] and v [heads, v_head_dim] from the input, each through a causal
+    convolution over `conv` rows per channel and silu; q and k made unit vectors per head
+    (x / sqrt(sum x^2 + `unit_eps`)), q times head_dim^-1/2; step size beta = sigmoid(b h) and decay
+    g = exp(-exp(A_log) softplus(a h + dt_bias)) per head. Per row: S <- g S; u = beta (v - S^T k);
+    S <- S + k u^T; o = S^T q. Each head's o is divided by its root mean square (`eps`), times the
+    weight `norm` [v_head_dim] (one for all heads), times silu(g h), then o. `weights`: q, k, v,
+    q_conv, k_conv, v_conv, b, a, A_log, dt_bias, norm, g, o.
+    """
+
+    hidden: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    conv: int
+    eps: float
+    weights: Mapping[str, str]
+    unit_eps: float = 1e-6
+    kind: str = "delta"
 
 
 @dataclass(frozen=True)
@@ -129,7 +190,8 @@ class BlockSpec:
     """The arrangement of one layer.
 
     kind "sandwich": norms `pre_mixer`, `post_mixer`, `pre_ffn`, `post_ffn` around both
-    branches; kind "prenorm": `pre_mixer` and `pre_ffn` only; kind "postnorm": the branches read
+    branches (`ffn` None: a layer of its mixer alone, with the first two norms);
+    kind "prenorm": `pre_mixer` and `pre_ffn` only; kind "postnorm": the branches read
     the residual itself and only their outputs are normed (`post_mixer`, `post_ffn`), and `ffn`
     may be None for a layer without a feed-forward.
     """
@@ -145,11 +207,26 @@ class ScheduleEntry:
     """One layer run: which layer, and whose cache it reads (its own when `cache_of == layer`).
 
     A layer named twice runs twice; a layer whose `cache_of` is another layer's index reads
-    that layer's keys and values and writes none.
+    that layer's keys and values and writes none. `replica` > 0 gives a run of the same layer a
+    cache (pages, state) of its own: a layer that runs several times with the same weights keeps
+    one cache a run. `before`: the spec of a part of category "merge" that rewrites the residual
+    stream ahead of this run (`InputMixSpec`), or None.
     """
 
     layer: int
     cache_of: int
+    replica: int = 0
+    before: Optional[object] = None
+
+
+@dataclass(frozen=True)
+class InputMixSpec:
+    """x <- W [x; x0]: the stream and the embedding's output x0 side by side through one matrix
+    `weight` [hidden, 2 hidden] (the stream's columns first)."""
+
+    hidden: int
+    weight: str
+    kind: str = "input_mix"
 
 
 @dataclass(frozen=True)

@@ -14,7 +14,9 @@
 // does not depend on the rest of the batch. With more than one chunk slot the blocks write
 // (sum p.v, max, sum p) to scratch memory and `combine_kernel` merges them in slot order. The
 // first `keep_slots` slots are the kept first keys' chunks, the others the window's. Values may
-// have another size than keys (`dv`).
+// have another size than keys (`dv`), and may lie `v_stride` apart: a value table that is the key
+// table itself, whose first `dv` components of a line are the value (attention through a latent).
+// With `sinks`, e^(sinks[head]) joins a row's denominator: a key without a value, not scaled.
 #pragma once
 #include "common.cuh"
 
@@ -59,7 +61,9 @@ struct AttParams {
     void* out;                // [rows, hq, dv]
     float* partial;           // [rows, hq, slots, dv + 2] or null when slots == 1
     int rows, hq, hkv, d, page_size, table_width, n_pages;
-    int dv;                   // the values' size (the v table is [pages, hkv, page_size, dv])
+    int dv;                   // the values' size (the v table is [pages, hkv, page_size, v_stride])
+    int v_stride;             // elements between two lines' values (dv, or more when values lie inside wider lines)
+    const float* sinks;       // [hq] or null: a term e^sink in the denominator of every row of the head
     int vec;                  // 1: a key is a whole number of 16-byte pieces and is loaded as such
     int window;               // 0: none
     int keep;                 // with a window: the keys [0, keep) stay visible below it
@@ -217,7 +221,7 @@ rows_kernel(const AttParams p) {
             for (int j = jstart; j < nkeys; j += tgroups) {
                 const int line = sline[j];
                 if (line < 0) continue;
-                const T* vp = vt + kv_row(line, kvh, p.hkv, p.page_size) * dv + 2 * pi;
+                const T* vp = vt + kv_row(line, kvh, p.hkv, p.page_size) * p.v_stride + 2 * pi;
                 const float v0 = Elem<T>::load(vp), v1 = 2 * pi + 1 < dv ? Elem<T>::load(vp + 1) : 0.f;
 #pragma unroll
                 for (int g = 0; g < GMAX; ++g) {
@@ -255,8 +259,15 @@ rows_kernel(const AttParams p) {
                 if (g >= gn) continue;
                 const int h = kvh * group + g0 + g;
                 if (p.slots == 1) {
-                    const float l = sstat[2 * g + 1];
-                    const float inv = l > 0.f ? 1.f / l : 0.f;
+                    float l = sstat[2 * g + 1];
+                    float inv = l > 0.f ? 1.f / l : 0.f;
+                    if (p.sinks != nullptr) {                   // the weights were taken against the keys' maximum m
+                        const float m = sstat[2 * g], sink = p.sinks[h];
+                        const float top = fmaxf(m, sink);
+                        const float wk = m == -INFINITY ? 0.f : soft_exp<T>(m - top);
+                        l = l * wk + soft_exp<T>(sink - top);
+                        inv = wk / l;
+                    }
                     T* o = out + ((size_t)r * p.hq + h) * dv + 2 * pi;
                     Elem<T>::store(o, acc[g][0] * inv);
                     if (2 * pi + 1 < dv) Elem<T>::store(o + 1, acc[g][1] * inv);
@@ -287,6 +298,10 @@ __global__ void combine_kernel(const AttParams p) {
         if (hi > lo) mx = fmaxf(mx, base[(size_t)z * (dv + 2) + dv]);
     }
     float denom = 0.f;
+    if (p.sinks != nullptr) {
+        mx = fmaxf(mx, p.sinks[h]);
+        denom = soft_exp<T>(p.sinks[h] - mx);
+    }
     for (int z = 0; z < p.slots; ++z) {
         int lo, hi;
         slot_range(p, count, z, lo, hi);

@@ -1,0 +1,288 @@
+// The gated delta rule, token by token, over the rows of a step.
+//
+// A head keeps a memory S [d, e] (d: key size, e: value size). With a decay g in (0, 1), a step size
+// beta in (0, 1), a unit key k, a unit query q (times d^-1/2) and a value v, a row does
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// so the read-out sees the row's own write. q, k (of `kv_heads` heads, shared by heads / kv_heads heads
+// each) and v come from a stacked product [rows, row_width] through a short causal convolution over
+// time, one filter a channel (`taps` weights, the last for the row itself, zeros before a request's
+// first row), and silu. g = exp(-exp(A_log) softplus(a + dt_bias)) and beta = sigmoid(b) come from two
+// more columns a head. The memory and the last taps - 1 inputs of every channel live in a slot of a
+// float32 state table, one slot a request, and are carried from a request's last row in this step to
+// its first row in the next. Everything here is 32-bit; only the projections may come in bfloat16.
+//
+// Three kernels. `delta_prep_kernel`, a block a row: convolution and silu of every channel (rows before
+// the step come from the slot's history), unit norms of q and k per head, q.k per kv head, decay and
+// step size per head, all left in 32-bit scratch. `delta_history_kernel`, a thread a channel of a
+// request: the slot's history becomes the last taps - 1 inputs. `delta_scan_kernel`: one block = one
+// request of the step x one head x DC value components, a warp a component, lane l the memory's rows
+// j = l, l + 32, ... of that column in registers. Written with the decayed memory M = g S of a row:
+// a = M.k and b = M.q are reduced side by side (one round of shuffles a row), u = beta (v - a),
+// o = b + u (k.q), S = M + k u. The next row's inputs are loaded while this one is reduced. A
+// column of a head's memory lies together in the state table, so a warp reads and writes whole lines.
+#include "common.cuh"
+
+namespace kb {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int DC = 4;                  // value components (warps) a block of the scan
+constexpr int DELTA_MAX_TAPS = 8;
+constexpr int DELTA_R = 8;             // memory rows a lane can hold: d <= 32 * DELTA_R
+
+struct DeltaParams {
+    int row_width;              // columns of the stacked product
+    int q_off, k_off, v_off, b_off, a_off;
+    const float* conv;          // [channels, taps]: q's channels, then k's, then v's
+    const float* a_log;         // [heads]
+    const float* dt_bias;       // [heads]
+    float* state;               // [slots, state_floats]: history [taps - 1, channels], then S [heads, e, d]
+    long long state_floats;
+    const int* row_entry;       // [rows]
+    const int* entry_start;     // [entries]
+    const int* entry_end;
+    const int* slots;           // [entries]; slot 0 belongs to rows that are no token's
+    int n_slots, entries, rows, heads, kv_heads, d, e, taps;
+    float q_scale, unit_eps;
+    float* qn;                  // [rows, kv_heads, d] scratch
+    float* kn;                  // [rows, kv_heads, d]
+    float* vn;                  // [rows, heads, e]
+    float* scal;                // [rows, heads, 2] decay, step size;
+    float* kq;                  // [rows, kv_heads]
+    float* out;                 // [rows, heads, e]
+};
+
+__device__ __forceinline__ float delta_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float delta_silu(float x) { return x / (1.f + expf(-x)); }
+
+template <typename TS>
+__global__ void __launch_bounds__(256)
+delta_prep_kernel(const Src<TS> src, const DeltaParams p) {
+    extern __shared__ float act[];                              // [channels]
+    const int r = blockIdx.x;
+    const int nq = p.kv_heads * p.d, nv = p.heads * p.e;
+    const int channels = 2 * nq + nv;
+    const int entry = p.row_entry[r];
+    int r0 = r, slot = 0;
+    if (entry >= 0 && entry < p.entries) {
+        r0 = p.entry_start[entry];
+        slot = p.slots[entry];
+    }
+    const bool kept = slot > 0 && slot < p.n_slots;
+    const float* hist = p.state + (size_t)(kept ? slot : 0) * p.state_floats;
+    const int taps = p.taps;
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        const int col = c < nq ? p.q_off + c : (c < 2 * nq ? p.k_off + (c - nq) : p.v_off + (c - 2 * nq));
+        float y = 0.f;
+        for (int j = 0; j < taps; ++j) {                        // the input j rows back
+            const int t = r - j;
+            float x;
+            if (t >= r0) x = src.at((size_t)t * p.row_width + col);
+            else if (kept) x = hist[(size_t)(taps - 1 + (t - r0)) * channels + c];     // t - r0 in [-(taps-1), -1]
+            else x = 0.f;
+            y = fmaf(p.conv[(size_t)c * taps + (taps - 1 - j)], x, y);
+        }
+        act[c] = delta_silu(y);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    // unit vectors per kv head, and q.k
+    for (int h = warp; h < p.kv_heads; h += warps) {
+        float sq = 0.f, sk = 0.f, qk = 0.f;
+        for (int i = lane; i < p.d; i += 32) {
+            const float q = act[h * p.d + i], k = act[nq + h * p.d + i];
+            sq = fmaf(q, q, sq);
+            sk = fmaf(k, k, sk);
+            qk = fmaf(q, k, qk);
+        }
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        qk = warp_sum(qk);
+        const float iq = p.q_scale / sqrtf(sq + p.unit_eps), ik = 1.f / sqrtf(sk + p.unit_eps);
+        for (int i = lane; i < p.d; i += 32) {
+            p.qn[((size_t)r * p.kv_heads + h) * p.d + i] = act[h * p.d + i] * iq;
+            p.kn[((size_t)r * p.kv_heads + h) * p.d + i] = act[nq + h * p.d + i] * ik;
+        }
+        if (lane == 0) p.kq[(size_t)r * p.kv_heads + h] = qk * iq * ik;
+    }
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) p.vn[(size_t)r * nv + i] = act[2 * nq + i];
+    for (int h = threadIdx.x; h < p.heads; h += blockDim.x) {
+        const float a = src.at((size_t)r * p.row_width + p.a_off + h) + p.dt_bias[h];
+        const float b = src.at((size_t)r * p.row_width + p.b_off + h);
+        p.scal[((size_t)r * p.heads + h) * 2] = expf(-expf(p.a_log[h]) * delta_softplus(a));
+        p.scal[((size_t)r * p.heads + h) * 2 + 1] = 1.f / (1.f + expf(-b));
+    }
+}
+
+// history <- the last taps - 1 inputs of (history, this step's rows), per channel of a request.
+template <typename TS>
+__global__ void delta_history_kernel(const Src<TS> src, const DeltaParams p) {
+    const int entry = blockIdx.y;
+    const int nq = p.kv_heads * p.d, nv = p.heads * p.e;
+    const int channels = 2 * nq + nv;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int r0 = p.entry_start[entry], r1 = p.entry_end[entry];
+    const int slot = p.slots[entry];
+    if (r1 <= r0 || slot <= 0 || slot >= p.n_slots) return;
+    const int keep = p.taps - 1;
+    if (keep <= 0) return;
+    float* hist = p.state + (size_t)slot * p.state_floats;
+    const int col = c < nq ? p.q_off + c : (c < 2 * nq ? p.k_off + (c - nq) : p.v_off + (c - 2 * nq));
+    const int n = r1 - r0;
+    float fresh[DELTA_MAX_TAPS];
+#pragma unroll
+    for (int i = 0; i < DELTA_MAX_TAPS; ++i) {
+        fresh[i] = 0.f;
+        if (i < keep) {
+            const int t = n - keep + i;                         // the input at this place, counted from the step's first row
+            fresh[i] = t >= 0 ? src.at((size_t)(r0 + t) * p.row_width + col) : hist[(size_t)(keep + t) * channels + c];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DELTA_MAX_TAPS; ++i)
+        if (i < keep) hist[(size_t)i * channels + c] = fresh[i];
+}
+
+template <int R>
+__global__ void __launch_bounds__(DC * 32)
+delta_scan_kernel(const DeltaParams p) {
+    const int entry = blockIdx.x, head = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.z * DC + warp;
+    const int r0 = p.entry_start[entry], r1 = p.entry_end[entry];
+    if (r1 <= r0 || c >= p.e) return;
+    const int slot = p.slots[entry];
+    const int d = p.d, e = p.e;
+    if (slot <= 0 || slot >= p.n_slots) {                       // rows of no request: zeros, no state
+        if (lane == 0)
+            for (int r = r0; r < r1; ++r) p.out[((size_t)r * p.heads + head) * e + c] = 0.f;
+        return;
+    }
+    const int nq = p.kv_heads * d, nv = p.heads * e;
+    const int kvh = head / (p.heads / p.kv_heads);
+    float* st = p.state + (size_t)slot * p.state_floats + (size_t)(p.taps - 1) * (2 * nq + nv) + ((size_t)head * e + c) * d;
+    float S[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] = lane + 32 * i < d ? st[lane + 32 * i] : 0.f;
+
+    float k[R], q[R], k2[R], q2[R];
+    float v, g, beta, kq, v2 = 0.f, g2 = 0.f, beta2 = 0.f, kq2 = 0.f;
+    auto fetch = [&](int r, float (&kk)[R], float (&qq)[R], float& vv, float& gg, float& bb, float& kkqq) {
+        const float* kp = p.kn + ((size_t)r * p.kv_heads + kvh) * d;
+        const float* qp = p.qn + ((size_t)r * p.kv_heads + kvh) * d;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int j = lane + 32 * i;
+            kk[i] = j < d ? kp[j] : 0.f;
+            qq[i] = j < d ? qp[j] : 0.f;
+        }
+        vv = p.vn[((size_t)r * p.heads + head) * e + c];
+        gg = p.scal[((size_t)r * p.heads + head) * 2];
+        bb = p.scal[((size_t)r * p.heads + head) * 2 + 1];
+        kkqq = p.kq[(size_t)r * p.kv_heads + kvh];
+    };
+    fetch(r0, k, q, v, g, beta, kq);
+    for (int r = r0; r < r1; ++r) {
+        if (r + 1 < r1) fetch(r + 1, k2, q2, v2, g2, beta2, kq2);
+        float a[2] = {0.f, 0.f}, b[2] = {0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            S[i] *= g;
+            a[i & 1] = fmaf(S[i], k[i], a[i & 1]);
+            b[i & 1] = fmaf(S[i], q[i], b[i & 1]);
+        }
+        float sa = a[0] + a[1], sb = b[0] + b[1];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            sa += __shfl_xor_sync(0xffffffffu, sa, o);
+            sb += __shfl_xor_sync(0xffffffffu, sb, o);
+        }
+        const float u = beta * (v - sa);
+#pragma unroll
+        for (int i = 0; i < R; ++i) S[i] = fmaf(k[i], u, S[i]);
+        if (lane == 0) p.out[((size_t)r * p.heads + head) * e + c] = fmaf(u, kq, sb);
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            k[i] = k2[i];
+            q[i] = q2[i];
+        }
+        v = v2; g = g2; beta = beta2; kq = kq2;
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+        if (lane + 32 * i < d) st[lane + 32 * i] = S[i];
+}
+
+}  // namespace kb
+
+using namespace kb;
+
+// Floats a request keeps between steps: the convolutions' history, then every head's memory.
+extern "C" long long kb_delta_state_floats(int heads, int kv_heads, int d, int e, int taps) {
+    return (long long)(taps - 1) * (2ll * kv_heads * d + (long long)heads * e) + (long long)heads * d * e;
+}
+
+// Floats of scratch for a step of `rows` rows: unit queries and keys, values, (decay, step size), q.k.
+extern "C" long long kb_delta_scratch_floats(int rows, int heads, int kv_heads, int d, int e) {
+    return (long long)rows * (2ll * kv_heads * d + (long long)heads * e + 2ll * heads + kv_heads);
+}
+
+extern "C" int kb_delta_scan(float* out, float* scratch, const void* src, int in_dt, int splits, long long split_stride, int row_width,
+                             int q_off, int k_off, int v_off, int b_off, int a_off, const float* conv, const float* a_log,
+                             const float* dt_bias, float* state, int n_slots, long long state_floats, const int* row_entry,
+                             const int* entry_start, const int* entry_end, const int* slots, int entries, int rows, int heads,
+                             int kv_heads, int d, int e, int taps, float q_scale, float unit_eps, void* stream) {
+    KB_REQUIRE(entries >= 0 && rows >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && d > 0 && e > 0,
+               "delta: entries %d, rows %d, heads %d over %d, sizes %d / %d", entries, rows, heads, kv_heads, d, e);
+    KB_REQUIRE(d <= 32 * DELTA_R, "delta: a key size of %d is more than the kernel's %d", d, 32 * DELTA_R);
+    KB_REQUIRE(taps >= 1 && taps <= DELTA_MAX_TAPS, "delta: a convolution of %d taps (1 to %d)", taps, DELTA_MAX_TAPS);
+    const long long nq = (long long)kv_heads * d, nv = (long long)heads * e;
+    KB_REQUIRE(row_width > 0 && q_off >= 0 && q_off + nq <= row_width && k_off >= 0 && k_off + nq <= row_width && v_off >= 0 &&
+                   v_off + nv <= row_width && b_off >= 0 && b_off + heads <= row_width && a_off >= 0 && a_off + heads <= row_width,
+               "delta: columns q %d, k %d, v %d, b %d, a %d do not fit a row of %d", q_off, k_off, v_off, b_off, a_off, row_width);
+    KB_REQUIRE(splits >= 1 && (splits == 1 || split_stride >= (long long)rows * row_width), "delta: %d slices %lld apart", splits, split_stride);
+    KB_REQUIRE(state_floats == kb_delta_state_floats(heads, kv_heads, d, e, taps), "delta: a state of %lld floats, expected %lld",
+               state_floats, kb_delta_state_floats(heads, kv_heads, d, e, taps));
+    KB_REQUIRE(n_slots >= 1 && state && scratch && out && conv && a_log && dt_bias && row_entry && entry_start && entry_end && slots,
+               "delta: state, scratch, weights or ranges are missing");
+    if (entries == 0 || rows == 0) return 0;
+    const long long channels = 2 * nq + nv;
+    KB_REQUIRE(channels * 4 <= 200 * 1024, "delta: %lld channels do not fit the shared memory of a block", channels);
+    KB_REQUIRE(heads <= 65535 && entries <= 65535 && (e + DC - 1) / DC <= 65535, "delta: too many heads, requests or value components for one launch");
+    DeltaParams p;
+    p.row_width = row_width; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.b_off = b_off; p.a_off = a_off;
+    p.conv = conv; p.a_log = a_log; p.dt_bias = dt_bias; p.state = state; p.state_floats = state_floats; p.row_entry = row_entry;
+    p.entry_start = entry_start; p.entry_end = entry_end; p.slots = slots; p.n_slots = n_slots; p.entries = entries; p.rows = rows;
+    p.heads = heads; p.kv_heads = kv_heads; p.d = d; p.e = e; p.taps = taps; p.q_scale = q_scale; p.unit_eps = unit_eps;
+    p.qn = scratch;
+    p.kn = p.qn + (size_t)rows * nq;
+    p.vn = p.kn + (size_t)rows * nq;
+    p.scal = p.vn + (size_t)rows * nv;
+    p.kq = p.scal + (size_t)rows * heads * 2;
+    p.out = out;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)channels * sizeof(float);
+#define KB_DELTA_PREP(TS)                                                                                                  \
+    do {                                                                                                                   \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        delta_prep_kernel<TS><<<rows, 256, smem, s>>>(Src<TS>{(const TS*)src, splits, (size_t)split_stride}, p);           \
+        if (int err = check_launch("delta prep")) return err;                                                              \
+        if (taps > 1) {                                                                                                    \
+            delta_history_kernel<TS><<<dim3((unsigned)((channels + 127) / 128), entries), 128, 0, s>>>(                     \
+                Src<TS>{(const TS*)src, splits, (size_t)split_stride}, p);                                                 \
+            if (int err = check_launch("delta history")) return err;                                                       \
+        }                                                                                                                  \
+    } while (0)
+    if (in_dt == KB_DT_F32) KB_DELTA_PREP(float);
+    else if (in_dt == KB_DT_BF16) KB_DELTA_PREP(bf16);
+    else return fail("delta: dtype code %d is not known", in_dt);
+#undef KB_DELTA_PREP
+    dim3 grid(entries, heads, (e + DC - 1) / DC);
+    const int need = (d + 31) / 32;
+    if (need <= 1) delta_scan_kernel<1><<<grid, DC * 32, 0, s>>>(p);
+    else if (need <= 2) delta_scan_kernel<2><<<grid, DC * 32, 0, s>>>(p);
+    else if (need <= 4) delta_scan_kernel<4><<<grid, DC * 32, 0, s>>>(p);
+    else delta_scan_kernel<DELTA_R><<<grid, DC * 32, 0, s>>>(p);
+    return check_launch("delta scan");
+}

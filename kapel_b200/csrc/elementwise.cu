@@ -29,13 +29,14 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
 }
 
 // ---------------------------------------------------------------------------------------
-// cos_sin[r, j] = (cos, sin)(positions[r] * theta^(-2j / rotary)), angle in 64-bit.
+// cos_sin[r, j] = (cos, sin)(positions[r] * theta^(-2j / rotary) / divisor), angle in 64-bit
+// (`divisor` 1: plain; f: every frequency divided by f, "linear scaling" of the positions).
 __global__ void rope_table_kernel(float2* __restrict__ cos_sin, const int* __restrict__ positions, int rows,
-                                  int half, int rotary, double theta) {
+                                  int half, int rotary, double theta, double divisor) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= rows * half) return;
     const int r = i / half, j = i % half;
-    const double w = pow(theta, -(2.0 * (double)j) / (double)rotary);
+    const double w = pow(theta, -(2.0 * (double)j) / (double)rotary) / divisor;
     const double a = (double)positions[r] * w;
     double s, c;
     sincos(a, &s, &c);
@@ -347,8 +348,9 @@ extern "C" int kb_embed(float* out, const void* table, int table_dt, const int* 
     return check_launch("embed");
 }
 
-extern "C" int kb_rope_table(float* cos_sin, const int* positions, int rows, int rotary, double theta,
+extern "C" int kb_rope_table(float* cos_sin, const int* positions, int rows, int rotary, double theta, double divisor,
                              void* stream) {
+    KB_REQUIRE(divisor > 0, "rope_table: the frequencies' divisor %g must be positive", divisor);
     KB_REQUIRE(rows >= 0 && rotary > 0 && rotary % 2 == 0, "rope_table: rows %d, rotary %d (must be even)", rows, rotary);
     KB_REQUIRE(theta > 0, "rope_table: theta %g must be positive", theta);
     if (rows == 0) return 0;
@@ -356,7 +358,7 @@ extern "C" int kb_rope_table(float* cos_sin, const int* positions, int rows, int
     const long long n = (long long)rows * half;
     KB_REQUIRE(n < (1ll << 31), "rope_table: %lld entries is too many", n);
     rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((float2*)cos_sin, positions, rows,
-                                                                                  half, rotary, theta);
+                                                                                  half, rotary, theta, divisor);
     return check_launch("rope_table");
 }
 
@@ -456,6 +458,28 @@ extern "C" int kb_pad_cols_bf16(void* out, const void* in, long long rows, int w
     KB_REQUIRE(blocks <= 0x7fffffffll, "pad_cols: too many values for one launch");
     pad_cols_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((bf16*)out, (const bf16*)in, rows, width, wide);
     return check_launch("pad_cols");
+}
+
+// out[r, :] = (a[r, :], b[r, :]) side by side, float32 in, `out_dt` out.
+template <typename TO>
+__global__ void concat2_kernel(TO* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b, long long rows, int width) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * 2 * width) return;
+    const long long r = i / (2 * width);
+    const int c = (int)(i - r * 2 * width);
+    Elem<TO>::store(out + i, c < width ? a[r * width + c] : b[r * width + (c - width)]);
+}
+extern "C" int kb_concat2(void* out, int out_dt, const float* a, const float* b, long long rows, int width, void* stream) {
+    KB_REQUIRE(rows >= 0 && width > 0, "concat2: rows %lld, width %d", rows, width);
+    if (rows == 0) return 0;
+    const long long n = rows * 2 * width;
+    KB_REQUIRE((n + 255) / 256 <= 0x7fffffffll, "concat2: too many values for one launch");
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dt == KB_DT_F32) concat2_kernel<float><<<blocks, 256, 0, s>>>((float*)out, a, b, rows, width);
+    else if (out_dt == KB_DT_BF16) concat2_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)out, a, b, rows, width);
+    else return fail("concat2: dtype code %d is not known", out_dt);
+    return check_launch("concat2");
 }
 
 extern "C" int kb_cast(void* out, int out_dt, const void* in, int in_dt, long long n, void* stream) {

@@ -9,8 +9,17 @@
 //                    weight over all heads) times sigmoid(gate[r, h, :]), the gate read from the
 //                    stacked product; the output's rows may be wider than the heads (zeros behind them).
 //  entry_ranges      first row and one past the last row of every request of a step, from the rows' entries.
+//  head_norm_rope_append  an RMS norm over every head's query and key (a weight of the head's size,
+//                    shared by the heads), then the rotation of the first `rotary` components, the
+//                    queries written out, keys and values (of their own size) to the paged cache.
+//  latent_append     for attention through latents: the query latent RMS-normed and written out; the
+//                    key/value latent RMS-normed and, behind it, the one rotated key part of the row,
+//                    written as the row's line of a cache with one kv head.
+//  head_linear       y[r, h, :] = x[r, h, :] . M[h] for a matrix a head ([heads, n_in, n_out]); optionally
+//                    a rotated copy of further components of x behind the product (the rotated part
+//                    of a latent query), or sigmoid(gate) on the result.
 //
-// Sums, norms and the sigmoid are 32-bit.
+// Sums, norms, rotations and the gates are 32-bit.
 #include "common.cuh"
 
 namespace kb {
@@ -71,7 +80,7 @@ __global__ void proj_norm_append_kernel(const Src<TS> src, int row_width, int q_
 template <typename TY, typename TS, typename TW, typename TO>
 __global__ void head_gate_kernel(TO* __restrict__ out, const TY* __restrict__ y, const Src<TS> gate, int row_width,
                                  int g_off, const TW* __restrict__ w, int unit, float eps, long long pairs, int heads, int e,
-                                 int out_stride) {
+                                 int out_stride, int act) {
     const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (pair >= pairs) return;
     const int lane = threadIdx.x & 31;
@@ -92,12 +101,184 @@ __global__ void head_gate_kernel(TO* __restrict__ out, const TY* __restrict__ y,
         float v = Elem<TY>::load(yp + c) * inv;
         if (w != nullptr) v *= Elem<TW>::load(w + (size_t)h * e + c);
         const float z = gate.at((size_t)r * row_width + g_off + (size_t)h * e + c);
-        v *= 1.f / (1.f + expf(-z));
+        v *= act == 1 ? z / (1.f + expf(-z)) : 1.f / (1.f + expf(-z));       // silu(z) or sigmoid(z)
         Elem<TO>::store(out + (size_t)r * out_stride + (size_t)h * e + c, v);
     }
     // a row wider than its heads (padding for the product that follows) ends in zeros
     if (h == heads - 1)
         for (int c = heads * e + lane; c < out_stride; c += 32) Elem<TO>::store(out + (size_t)r * out_stride + c, 0.f);
+}
+
+// One block a row; a warp takes head vectors in turn (queries, then keys, then values) through a
+// piece of shared memory of its own.
+template <typename TS, typename TW, typename TO>
+__global__ void head_norm_rope_append_kernel(const Src<TS> src, int row_width, int q_off, int k_off, int v_off,
+                                             const TW* __restrict__ wq, float eps_q, float off_q,
+                                             const TW* __restrict__ wk, float eps_k, float off_k,
+                                             const float2* __restrict__ cos_sin, int rotary,
+                                             const int* __restrict__ lines, TO* __restrict__ q_out, TO* __restrict__ k_table,
+                                             TO* __restrict__ v_table, int hq, int hkv, int d, int dv, long long table_lines,
+                                             int page_size) {
+    extern __shared__ float vecs[];                             // [warps][d]
+    const int r = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    float* x = vecs + (size_t)warp * d;
+    const size_t base = (size_t)r * row_width;
+    const int half = rotary >> 1;
+    long long line = -1;
+    if (k_table != nullptr) {
+        line = lines[r];
+        if (line >= table_lines) line = -1;
+    }
+    for (int u = warp; u < hq + hkv; u += warps) {
+        const bool is_q = u < hq;
+        const int h = is_q ? u : u - hq;
+        if (!is_q && line < 0) continue;                        // a row that writes nowhere
+        const size_t at = base + (is_q ? q_off : k_off) + (size_t)h * d;
+        const TW* w = is_q ? wq : wk;
+        float ss = 0.f;
+        for (int i = lane; i < d; i += 32) {
+            const float v = src.at(at + i);
+            x[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+        if (w != nullptr) {
+            ss = warp_sum(ss);
+            const float inv = 1.f / sqrtf(ss / (float)d + (is_q ? eps_q : eps_k));
+            const float off = is_q ? off_q : off_k;
+            for (int i = lane; i < d; i += 32) x[i] = x[i] * inv * (off + Elem<TW>::load(w + i));
+        }
+        __syncwarp();
+        for (int i = lane; i < half; i += 32) {
+            float a = x[i], b = x[i + half];
+            rope_rotate(a, b, cos_sin[(size_t)r * half + i]);
+            x[i] = a;
+            x[i + half] = b;
+        }
+        __syncwarp();
+        TO* dst = is_q ? q_out + ((size_t)r * hq + h) * d : k_table + kv_row(line, h, hkv, page_size) * d;
+        for (int i = lane; i < d; i += 32) Elem<TO>::store(dst + i, x[i]);
+        __syncwarp();
+    }
+    if (line < 0) return;
+    for (int i = threadIdx.x; i < hkv * dv; i += blockDim.x) {
+        const int h = i / dv, c = i - h * dv;
+        Elem<TO>::store(v_table + kv_row(line, h, hkv, page_size) * dv + c, src.at(base + v_off + i));
+    }
+}
+
+// One block a row. The cache has one kv head whose line is [latent (kv_rank) | rotated part (rot)].
+template <typename TS, typename TW, typename TO>
+__global__ void latent_append_kernel(const Src<TS> src, int row_width, int q_off, int kv_off, int q_rank, int kv_rank, int rot,
+                                     const TW* __restrict__ wq, const TW* __restrict__ wkv, float eps,
+                                     const float2* __restrict__ cos_sin, const int* __restrict__ lines,
+                                     TO* __restrict__ cq_out, int cq_stride, TO* __restrict__ k_table, long long table_lines,
+                                     int page_size) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const size_t base = (size_t)r * row_width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
+        const float v = src.at(base + q_off + i);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv_q = 1.f / sqrtf(ss / (float)q_rank + eps);
+    for (int i = threadIdx.x; i < cq_stride; i += blockDim.x) {
+        const float v = i < q_rank ? src.at(base + q_off + i) * inv_q * Elem<TW>::load(wq + i) : 0.f;
+        Elem<TO>::store(cq_out + (size_t)r * cq_stride + i, v);
+    }
+    if (k_table == nullptr) return;
+    const long long line = lines[r];
+    if (line < 0 || line >= table_lines) return;                // a row that writes nowhere (padding)
+    float sk = 0.f;
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) {
+        const float v = src.at(base + kv_off + i);
+        sk = fmaf(v, v, sk);
+    }
+    sk = block_sum(sk, scratch);
+    const float inv_k = 1.f / sqrtf(sk / (float)kv_rank + eps);
+    TO* dst = k_table + kv_row(line, 0, 1, page_size) * (kv_rank + rot);
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x)
+        Elem<TO>::store(dst + i, src.at(base + kv_off + i) * inv_k * Elem<TW>::load(wkv + i));
+    const int half = rot >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float a = src.at(base + kv_off + kv_rank + i), b = src.at(base + kv_off + kv_rank + i + half);
+        rope_rotate(a, b, cos_sin[(size_t)r * half + i]);
+        Elem<TO>::store(dst + kv_rank + i, a);
+        Elem<TO>::store(dst + kv_rank + i + half, b);
+    }
+}
+
+// y[r, h, c] = sum_i x[r, h, i] M[h, i, c]. One block = HL_ROWS rows x one head x HL_COLS columns; the rows'
+// inputs lie in shared memory, a thread owns a column and walks M[h, :, c] (neighbours read neighbours).
+constexpr int HL_ROWS = 8;
+constexpr int HL_COLS = 128;
+template <typename TX, typename T>
+__global__ void __launch_bounds__(HL_COLS)
+head_linear_kernel(T* __restrict__ y, int y_row, int y_head, const Src<TX> x, int x_row, int x_head, int x_off,
+                   const T* __restrict__ m, int n_in, int n_out, int rows, int heads,
+                   int tail_off, int tail, const float2* __restrict__ cos_sin,
+                   const Src<float> gate, int g_row, int g_off) {
+    extern __shared__ float xs[];                               // [HL_ROWS][n_in]
+    const int rbase = blockIdx.x * HL_ROWS, h = blockIdx.y;
+    const int nr = min(HL_ROWS, rows - rbase);
+    for (int idx = threadIdx.x; idx < HL_ROWS * n_in; idx += HL_COLS) {
+        const int t = idx / n_in, i = idx - t * n_in;
+        xs[idx] = t < nr ? x.at((size_t)(rbase + t) * x_row + (size_t)h * x_head + x_off + i) : 0.f;
+    }
+    __syncthreads();
+    const int c = blockIdx.z * HL_COLS + threadIdx.x;
+    if (c < n_out) {
+        float acc[HL_ROWS];
+#pragma unroll
+        for (int t = 0; t < HL_ROWS; ++t) acc[t] = 0.f;
+        const T* col = m + (size_t)h * n_in * n_out + c;
+        int i = 0;
+        for (; i + 4 <= n_in; i += 4) {                         // four loads in flight
+            float w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = Elem<T>::load(col + (size_t)(i + j) * n_out);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int t = 0; t < HL_ROWS; ++t) acc[t] = fmaf(xs[t * n_in + i + j], w[j], acc[t]);
+        }
+        for (; i < n_in; ++i) {
+            const float w = Elem<T>::load(col + (size_t)i * n_out);
+#pragma unroll
+            for (int t = 0; t < HL_ROWS; ++t) acc[t] = fmaf(xs[t * n_in + i], w, acc[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < HL_ROWS; ++t) {
+            if (t >= nr) continue;
+            float v = acc[t];
+            if (gate.p != nullptr) {
+                const float z = gate.at((size_t)(rbase + t) * g_row + g_off + (size_t)h * n_out + c);
+                v *= 1.f / (1.f + expf(-z));
+            }
+            Elem<T>::store(y + (size_t)(rbase + t) * y_row + (size_t)h * y_head + c, v);
+        }
+    }
+    if (blockIdx.z != 0) return;
+    // behind the product: `tail` further components of x, rotated
+    const int half = tail >> 1;
+    for (int idx = threadIdx.x; idx < nr * half; idx += HL_COLS) {
+        const int t = idx / half, i = idx - t * half;
+        const size_t at = (size_t)(rbase + t) * x_row + (size_t)h * x_head + tail_off;
+        float a = x.at(at + i), b = x.at(at + i + half);
+        rope_rotate(a, b, cos_sin[(size_t)(rbase + t) * half + i]);
+        T* dst = y + (size_t)(rbase + t) * y_row + (size_t)h * y_head + n_out;
+        Elem<T>::store(dst + i, a);
+        Elem<T>::store(dst + i + half, b);
+    }
+    // a row wider than its heads (padding for the product that follows) ends in zeros
+    if (h == heads - 1)
+        for (int idx = threadIdx.x; idx < nr * (y_row - heads * y_head); idx += HL_COLS) {
+            const int pad = y_row - heads * y_head;
+            const int t = idx / pad, i = idx - t * pad;
+            Elem<T>::store(y + (size_t)(rbase + t) * y_row + heads * y_head + i, 0.f);
+        }
 }
 
 __global__ void entry_ranges_clear_kernel(int entries, int* __restrict__ start, int* __restrict__ end) {
@@ -170,8 +351,9 @@ extern "C" int kb_proj_norm_append(const void* src, int in_dt, int splits, long 
 
 extern "C" int kb_head_gate(void* out, int out_dt, const void* y, int y_dt, const void* gate, int g_dt, int splits,
                             long long split_stride, int row_width, int g_off, const void* w, int w_dt, int unit, float eps,
-                            long long rows, int heads, int e, int out_stride, void* stream) {
+                            long long rows, int heads, int e, int out_stride, int act, void* stream) {
     KB_REQUIRE(rows >= 0 && heads > 0 && e > 0, "head_gate: rows %lld, heads %d of %d", rows, heads, e);
+    KB_REQUIRE(act == 0 || act == 1, "head_gate: gate activation code %d is not known (0 sigmoid, 1 silu)", act);
     KB_REQUIRE(out_stride >= heads * e, "head_gate: output rows of %d values for %d heads of %d", out_stride, heads, e);
     KB_REQUIRE(row_width > 0 && g_off >= 0 && g_off + heads * e <= row_width, "head_gate: gate columns %d.. do not fit a row of %d", g_off, row_width);
     KB_REQUIRE(splits >= 1 && (splits == 1 || split_stride >= rows * row_width), "head_gate: %d slices %lld apart", splits, split_stride);
@@ -184,7 +366,7 @@ extern "C" int kb_head_gate(void* out, int out_dt, const void* y, int y_dt, cons
 #define KB_HG(TY, TS, TW, TO)                                                                                       \
     head_gate_kernel<TY, TS, TW, TO><<<(unsigned)blocks, warps * 32, 0, s>>>((TO*)out, (const TY*)y,                    \
                                                                              Src<TS>{(const TS*)gate, splits, (size_t)split_stride}, \
-                                                                             row_width, g_off, (const TW*)w, unit, eps, pairs, heads, e, out_stride)
+                                                                             row_width, g_off, (const TW*)w, unit, eps, pairs, heads, e, out_stride, act)
     const int code = y_dt * 8 + g_dt * 4 + w_dt * 2 + out_dt;
     switch (code) {
         case 0: KB_HG(float, float, float, float); break;
@@ -207,4 +389,117 @@ extern "C" int kb_head_gate(void* out, int out_dt, const void* y, int y_dt, cons
     }
 #undef KB_HG
     return check_launch("head_gate");
+}
+
+extern "C" int kb_head_norm_rope_append(const void* src, int in_dt, int splits, long long split_stride, int row_width, int q_off,
+                                        int k_off, int v_off, const void* wq, float eps_q, float off_q, const void* wk,
+                                        float eps_k, float off_k, int w_dt, const float* cos_sin, int rotary, const int* lines,
+                                        void* q_out, void* k_table, void* v_table, int out_dt, int rows, int hq, int hkv, int d,
+                                        int dv, int write_kv, long long table_lines, int page_size, void* stream) {
+    KB_REQUIRE(rows >= 0 && hq > 0 && hkv > 0 && d > 0 && dv > 0, "head_norm_rope_append: rows %d, heads %d / %d, sizes %d / %d", rows, hq, hkv, d, dv);
+    KB_REQUIRE(rotary >= 0 && rotary <= d && rotary % 2 == 0, "head_norm_rope_append: rotary %d must be even and at most the head's %d", rotary, d);
+    KB_REQUIRE(rotary == 0 || cos_sin != nullptr, "head_norm_rope_append: a rotation without its table");
+    KB_REQUIRE(row_width > 0 && q_off >= 0 && q_off + hq * d <= row_width && k_off >= 0 && k_off + hkv * d <= row_width &&
+                   v_off >= 0 && v_off + hkv * dv <= row_width,
+               "head_norm_rope_append: columns q %d, k %d, v %d do not fit a row of %d", q_off, k_off, v_off, row_width);
+    KB_REQUIRE(splits >= 1 && (splits == 1 || split_stride >= (long long)rows * row_width), "head_norm_rope_append: %d slices %lld apart", splits, split_stride);
+    KB_REQUIRE(!write_kv || (lines && k_table && v_table && table_lines > 0 && page_size > 0), "head_norm_rope_append: no cache to write");
+    KB_REQUIRE(d <= 4096, "head_norm_rope_append: a head of %d components", d);
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    void* kt = write_kv ? k_table : nullptr;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * d * sizeof(float);
+#define KB_HNRA(TS, TW, TO)                                                                                              \
+    head_norm_rope_append_kernel<TS, TW, TO><<<rows, warps * 32, smem, s>>>(                                                 \
+        Src<TS>{(const TS*)src, splits, (size_t)split_stride}, row_width, q_off, k_off, v_off, (const TW*)wq, eps_q, off_q,  \
+        (const TW*)wk, eps_k, off_k, (const float2*)cos_sin, rotary, lines, (TO*)q_out, (TO*)kt, (TO*)v_table, hq, hkv, d, dv, \
+        table_lines, page_size)
+    const int code = in_dt * 4 + w_dt * 2 + out_dt;
+    switch (code) {
+        case 0: KB_HNRA(float, float, float); break;
+        case 1: KB_HNRA(float, float, bf16); break;
+        case 2: KB_HNRA(float, bf16, float); break;
+        case 3: KB_HNRA(float, bf16, bf16); break;
+        case 4: KB_HNRA(bf16, float, float); break;
+        case 5: KB_HNRA(bf16, float, bf16); break;
+        case 6: KB_HNRA(bf16, bf16, float); break;
+        case 7: KB_HNRA(bf16, bf16, bf16); break;
+        default: return fail("head_norm_rope_append: dtype codes in %d, w %d, out %d are not known", in_dt, w_dt, out_dt);
+    }
+#undef KB_HNRA
+    return check_launch("head_norm_rope_append");
+}
+
+extern "C" int kb_latent_append(const void* src, int in_dt, int splits, long long split_stride, int row_width, int q_off, int kv_off,
+                                int q_rank, int kv_rank, int rot, const void* wq, const void* wkv, int w_dt, float eps,
+                                const float* cos_sin, const int* lines, void* cq_out, int cq_stride, void* k_table, int out_dt,
+                                int rows, int write_kv, long long table_lines, int page_size, void* stream) {
+    KB_REQUIRE(rows >= 0 && q_rank > 0 && kv_rank > 0 && rot >= 0 && rot % 2 == 0, "latent_append: rows %d, ranks %d / %d, rotated %d", rows, q_rank, kv_rank, rot);
+    KB_REQUIRE(row_width > 0 && q_off >= 0 && q_off + q_rank <= row_width && kv_off >= 0 && kv_off + kv_rank + rot <= row_width,
+               "latent_append: columns q %d, kv %d do not fit a row of %d", q_off, kv_off, row_width);
+    KB_REQUIRE(splits >= 1 && (splits == 1 || split_stride >= (long long)rows * row_width), "latent_append: %d slices %lld apart", splits, split_stride);
+    KB_REQUIRE(cq_stride >= q_rank && wq && wkv && cq_out, "latent_append: output rows of %d for a latent of %d, or a weight is missing", cq_stride, q_rank);
+    KB_REQUIRE(rot == 0 || cos_sin != nullptr, "latent_append: a rotation without its table");
+    KB_REQUIRE(!write_kv || (lines && k_table && table_lines > 0 && page_size > 0), "latent_append: no cache to write");
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    void* kt = write_kv ? k_table : nullptr;
+#define KB_LA(TS, TW, TO)                                                                                                  \
+    latent_append_kernel<TS, TW, TO><<<rows, 128, 0, s>>>(Src<TS>{(const TS*)src, splits, (size_t)split_stride}, row_width, q_off, \
+                                                          kv_off, q_rank, kv_rank, rot, (const TW*)wq, (const TW*)wkv, eps,     \
+                                                          (const float2*)cos_sin, lines, (TO*)cq_out, cq_stride, (TO*)kt,       \
+                                                          table_lines, page_size)
+    const int code = in_dt * 4 + w_dt * 2 + out_dt;
+    switch (code) {
+        case 0: KB_LA(float, float, float); break;
+        case 1: KB_LA(float, float, bf16); break;
+        case 2: KB_LA(float, bf16, float); break;
+        case 3: KB_LA(float, bf16, bf16); break;
+        case 4: KB_LA(bf16, float, float); break;
+        case 5: KB_LA(bf16, float, bf16); break;
+        case 6: KB_LA(bf16, bf16, float); break;
+        case 7: KB_LA(bf16, bf16, bf16); break;
+        default: return fail("latent_append: dtype codes in %d, w %d, out %d are not known", in_dt, w_dt, out_dt);
+    }
+#undef KB_LA
+    return check_launch("latent_append");
+}
+
+// x: `x_dt`, maybe split-K partial sums; m and y: `dt`; gate: float32 (maybe partial sums) or null.
+extern "C" int kb_head_linear(void* y, int dt, int y_row, int y_head, const void* x, int x_dt, int x_splits, long long x_split_stride,
+                              int x_row, int x_head, int x_off, const void* m, int n_in, int n_out, int rows, int heads,
+                              int tail_off, int tail, const float* cos_sin, const float* gate, int g_splits,
+                              long long g_split_stride, int g_row, int g_off, void* stream) {
+    KB_REQUIRE(rows >= 0 && heads > 0 && n_in > 0 && n_out > 0, "head_linear: rows %d, heads %d, sizes %d -> %d", rows, heads, n_in, n_out);
+    KB_REQUIRE(tail >= 0 && tail % 2 == 0 && (tail == 0 || cos_sin != nullptr), "head_linear: %d rotated components (even, with a table)", tail);
+    KB_REQUIRE(y_head >= n_out + tail && y_row >= heads * y_head, "head_linear: output rows of %d, heads of %d for %d + %d values", y_row, y_head, n_out, tail);
+    KB_REQUIRE(x_off >= 0 && x_off + n_in <= x_head && (tail == 0 || (tail_off >= 0 && tail_off + tail <= x_head)) && x_row >= heads * x_head,
+               "head_linear: input rows of %d, heads of %d, columns %d.. and %d..", x_row, x_head, x_off, tail_off);
+    KB_REQUIRE(x_splits >= 1 && (x_splits == 1 || x_split_stride >= (long long)rows * x_row), "head_linear: %d slices %lld apart", x_splits, x_split_stride);
+    KB_REQUIRE(gate == nullptr || (g_splits >= 1 && g_off >= 0 && g_off + heads * n_out <= g_row), "head_linear: gate columns %d.. of a row of %d", g_off, g_row);
+    const size_t smem = (size_t)HL_ROWS * n_in * sizeof(float);
+    KB_REQUIRE(smem <= 200 * 1024, "head_linear: %d inputs a head do not fit the shared memory of a block", n_in);
+    KB_REQUIRE(heads <= 65535 && (n_out + HL_COLS - 1) / HL_COLS <= 65535, "head_linear: too many heads or columns for one launch");
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid((rows + HL_ROWS - 1) / HL_ROWS, heads, (n_out + HL_COLS - 1) / HL_COLS);
+    const Src<float> g{gate, gate ? g_splits : 1, (size_t)g_split_stride};
+#define KB_HL(TX, T)                                                                                                       \
+    do {                                                                                                                   \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(head_linear_kernel<TX, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        head_linear_kernel<TX, T><<<grid, HL_COLS, smem, s>>>((T*)y, y_row, y_head, Src<TX>{(const TX*)x, x_splits, (size_t)x_split_stride}, \
+                                                            x_row, x_head, x_off, (const T*)m, n_in, n_out, rows, heads, tail_off, \
+                                                            tail, (const float2*)cos_sin, g, g_row, g_off);                 \
+    } while (0)
+    const int code = x_dt * 2 + dt;
+    switch (code) {
+        case 0: KB_HL(float, float); break;
+        case 1: KB_HL(float, bf16); break;
+        case 2: KB_HL(bf16, float); break;
+        case 3: KB_HL(bf16, bf16); break;
+        default: return fail("head_linear: dtype codes x %d, weights %d are not known", x_dt, dt);
+    }
+#undef KB_HL
+    return check_launch("head_linear");
 }

@@ -502,6 +502,85 @@ __global__ void add_rmsnorm_splits_bulk_kernel(float* __restrict__ residual, con
     KB_TL_LEAVE(norm, blockIdx.x == 0, 0);
 }
 
+// ---------------------------------------------------------------------------------------
+// Norms that may take the mean off first (a layer norm with a weight and no bias):
+// y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * (offset + w); without `center` the RMS norm above.
+// The variance is the mean of the squared deviations, taken in a second walk over the row.
+template <typename TX, typename TW, typename TY>
+__global__ void centered_norm_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __restrict__ w, int width,
+                                     float eps, float offset) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * width;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) sum += Elem<TX>::load(x + base + i);
+    const float mean = block_sum(sum, scratch) / (float)width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = Elem<TX>::load(x + base + i) - mean;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = Elem<TX>::load(x + base + i) - mean;
+        Elem<TY>::store(y + base + i, v * inv * (offset + Elem<TW>::load(w + i)));
+    }
+}
+
+// residual += norm_post(branch); then h = norm_next(residual) (or, without a next norm, the sum itself
+// where an output is given). Either norm may be centered. The row lies in shared memory between the
+// walks: the branch, possibly many split-K slices, is read once, and the residual once.
+template <typename TB, typename TW, typename TH>
+__global__ void add_norm_centered_kernel(float* __restrict__ residual, const Src<TB> branch,
+                                         const TW* __restrict__ w_post, float eps_post, float off_post, int center_post,
+                                         const TW* __restrict__ w_next, float eps_next, float off_next, int center_next,
+                                         TH* __restrict__ h, int width) {
+    extern __shared__ float row[];                              // [width]
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * width;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float b = branch.at(base + i);
+        row[i] = b;
+        sum += b;
+    }
+    float mean = 0.f, inv = 1.f;
+    if (w_post != nullptr) {
+        if (center_post) mean = block_sum(sum, scratch) / (float)width;
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float v = row[i] - mean;
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        inv = 1.f / sqrtf(ss / (float)width + eps_post);
+    }
+    float sum2 = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float b = row[i];
+        if (w_post != nullptr) b = (b - mean) * inv * (off_post + Elem<TW>::load(w_post + i));
+        const float r = residual[base + i] + b;
+        residual[base + i] = r;
+        row[i] = r;
+        sum2 += r;
+    }
+    if (w_next == nullptr) {
+        if (h != nullptr)
+            for (int i = threadIdx.x; i < width; i += blockDim.x) Elem<TH>::store(h + base + i, row[i]);
+        return;
+    }
+    const float mean2 = center_next ? block_sum(sum2, scratch) / (float)width : 0.f;
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = row[i] - mean2;
+        ss2 += v * v;
+    }
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.f / sqrtf(ss2 / (float)width + eps_next);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        Elem<TH>::store(h + base + i, (row[i] - mean2) * inv2 * (off_next + Elem<TW>::load(w_next + i)));
+}
+
 static int threads_for(int width) { return width >= 2048 ? 512 : (width >= 512 ? 256 : 128); }
 
 }  // namespace kb
@@ -626,4 +705,70 @@ extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt
     }
 #undef KB_ADDNORM
     return check_launch("add_rmsnorm");
+}
+
+
+// The centered norm alone. x: f32 or bf16; w: f32 or bf16; y: f32 or bf16.
+extern "C" int kb_layernorm(void* y, int y_dt, const void* x, int x_dt, const void* w, int w_dt, int rows, int width,
+                            float eps, float offset, void* stream) {
+    KB_REQUIRE(rows >= 0 && width > 0, "layernorm: rows %d, width %d", rows, width);
+    KB_REQUIRE(eps >= 0.f, "layernorm: eps %g is negative", eps);
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int t = threads_for(width);
+#define KB_LNORM(TX, TW, TY) \
+    centered_norm_kernel<TX, TW, TY><<<rows, t, 0, s>>>((TY*)y, (const TX*)x, (const TW*)w, width, eps, offset)
+    const int code = x_dt * 4 + w_dt * 2 + y_dt;
+    switch (code) {
+        case 0: KB_LNORM(float, float, float); break;
+        case 1: KB_LNORM(float, float, bf16); break;
+        case 2: KB_LNORM(float, bf16, float); break;
+        case 3: KB_LNORM(float, bf16, bf16); break;
+        case 4: KB_LNORM(bf16, float, float); break;
+        case 5: KB_LNORM(bf16, float, bf16); break;
+        case 6: KB_LNORM(bf16, bf16, float); break;
+        case 7: KB_LNORM(bf16, bf16, bf16); break;
+        default: return fail("layernorm: dtype codes x %d, w %d, y %d are not known", x_dt, w_dt, y_dt);
+    }
+#undef KB_LNORM
+    return check_launch("layernorm");
+}
+
+// As kb_add_rmsnorm, with each norm centered or not (`center_post`, `center_next`).
+extern "C" int kb_add_norm(float* residual, const void* branch, int branch_dt, int splits, long long split_stride,
+                           const void* w_post, float eps_post, float off_post, int center_post, const void* w_next,
+                           float eps_next, float off_next, int center_next, void* h, int h_dt, int w_dt, int rows, int width,
+                           void* stream) {
+    if (!(w_post && center_post) && !(w_next && center_next))
+        return kb_add_rmsnorm(residual, branch, branch_dt, splits, split_stride, w_post, eps_post, off_post, w_next, eps_next,
+                              off_next, h, h_dt, w_dt, rows, width, stream);
+    KB_REQUIRE(rows >= 0 && width > 0, "add_norm: rows %d, width %d", rows, width);
+    KB_REQUIRE(w_next == nullptr || h != nullptr, "add_norm: a following norm needs an output");
+    KB_REQUIRE(splits >= 1 && (splits == 1 || split_stride >= (long long)rows * width), "add_norm: %d slices %lld apart", splits, split_stride);
+    const size_t smem = (size_t)width * sizeof(float);
+    KB_REQUIRE(smem <= 200 * 1024, "add_norm: a row of %d values does not fit the shared memory of a block", width);
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int t = threads_for(width);
+#define KB_ADDLN(TB, TW, TH)                                                                                              \
+    do {                                                                                                                  \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(add_norm_centered_kernel<TB, TW, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        add_norm_centered_kernel<TB, TW, TH><<<rows, t, smem, s>>>(residual, Src<TB>{(const TB*)branch, splits, (size_t)split_stride}, \
+                                                                 (const TW*)w_post, eps_post, off_post, center_post,        \
+                                                                 (const TW*)w_next, eps_next, off_next, center_next, (TH*)h, width); \
+    } while (0)
+    const int code = branch_dt * 4 + w_dt * 2 + h_dt;
+    switch (code) {
+        case 0: KB_ADDLN(float, float, float); break;
+        case 1: KB_ADDLN(float, float, bf16); break;
+        case 2: KB_ADDLN(float, bf16, float); break;
+        case 3: KB_ADDLN(float, bf16, bf16); break;
+        case 4: KB_ADDLN(bf16, float, float); break;
+        case 5: KB_ADDLN(bf16, float, bf16); break;
+        case 6: KB_ADDLN(bf16, bf16, float); break;
+        case 7: KB_ADDLN(bf16, bf16, bf16); break;
+        default: return fail("add_norm: dtype codes branch %d, w %d, h %d are not known", branch_dt, w_dt, h_dt);
+    }
+#undef KB_ADDLN
+    return check_launch("add_norm");
 }

@@ -61,7 +61,7 @@ def library():
                 lib = ctypes.CDLL(str(path))
                 lib.kb_last_error.restype = ctypes.c_char_p
                 for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats", "kb_sample_scratch_floats",
-                             "kb_mlstm_state_floats"):
+                             "kb_mlstm_state_floats", "kb_delta_state_floats", "kb_delta_scratch_floats"):
                     getattr(lib, name).restype = ctypes.c_longlong
                 lib.kb_launch_count.restype = ctypes.c_ulonglong
                 lib.kb_set_pdl(1 if PDL else 0)
@@ -258,12 +258,14 @@ def embed(table: torch.Tensor, ids: torch.Tensor, scale: float, out: Optional[to
     return out
 
 
-def rope_table(positions: torch.Tensor, rotary: int, theta: float) -> torch.Tensor:
-    """[rows, rotary/2, 2] float32 of (cos, sin); angles in float64 on the device."""
+def rope_table(positions: torch.Tensor, rotary: int, theta: float, divisor: float = 1.0) -> torch.Tensor:
+    """[rows, rotary/2, 2] float32 of (cos, sin); angles in float64 on the device. Every frequency
+    theta^(-2j/rotary) is divided by `divisor` (1: the plain rotation)."""
     _need(positions, "rope positions", torch.int32)
     rows = positions.numel()
     out = _fresh((rows, rotary // 2, 2), torch.float32, positions.device)
-    _check(library().kb_rope_table(_ptr(out), _ptr(positions), rows, int(rotary), ctypes.c_double(float(theta)), _stream()))
+    _check(library().kb_rope_table(_ptr(out), _ptr(positions), rows, int(rotary), ctypes.c_double(float(theta)), ctypes.c_double(float(divisor)),
+                                  _stream()))
     return out
 
 
@@ -350,18 +352,44 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float, ou
     return y
 
 
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """(x - mean) / sqrt(mean((x - mean)^2) + eps) * (offset + weight) over each row, in 32-bit."""
+    _need(x, "layernorm input")
+    rows, width = x.shape
+    _need(weight, "layernorm weight", shape=(width,))
+    y = _fresh((rows, width), out_dtype, x.device)
+    _check(
+        library().kb_layernorm(_ptr(y), _dt(y, "layernorm output"), _ptr(x), _dt(x, "layernorm input"), _ptr(weight),
+                               _dt(weight, "layernorm weight"), rows, width, _f(eps), _f(offset), _stream())
+    )
+    return y
+
+
+def concat2(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """[rows, 2 width]: the float32 rows of `a` and of `b` side by side, in `out_dtype`."""
+    _need(a, "concat2 first", torch.float32)
+    _need(b, "concat2 second", torch.float32, tuple(a.shape))
+    rows, width = a.shape
+    out = _fresh((rows, 2 * width), out_dtype, a.device)
+    _check(library().kb_concat2(_ptr(out), _CODES[out_dtype], _ptr(a), _ptr(b), ctypes.c_longlong(rows), int(width), _stream()))
+    return out
+
+
 def add_rmsnorm(residual, branch, post, nxt, out_dtype, copy_out: bool = False):
     """residual += norm_post(branch) (post = (weight, eps, offset) or None: plain add); returns
     norm_next(residual) when nxt = (weight, eps, offset) is given; without it, None, or with
     `copy_out` the new residual itself in `out_dtype` (what a reader of the residual takes next).
-    In place on residual. `branch` is a tensor or a SplitSum."""
+    A fourth value True in either tuple makes that norm take the row's mean off first (a layer
+    norm with a weight and no bias). In place on residual. `branch` is a tensor or a SplitSum."""
     rows, width = residual.shape
     _need(residual, "add_rmsnorm residual", torch.float32)
     src, b_dt, splits, stride = _src(branch, "add_rmsnorm branch")
     if tuple(branch.shape) != (rows, width):
         raise KernelError(f"add_rmsnorm: branch {tuple(branch.shape)} against residual {(rows, width)}")
-    w_post, eps_post, off_post = post if post is not None else (None, 0.0, 0.0)
-    w_next, eps_next, off_next = nxt if nxt is not None else (None, 0.0, 0.0)
+    w_post, eps_post, off_post = post[:3] if post is not None else (None, 0.0, 0.0)
+    w_next, eps_next, off_next = nxt[:3] if nxt is not None else (None, 0.0, 0.0)
+    center_post = bool(post is not None and len(post) > 3 and post[3])
+    center_next = bool(nxt is not None and len(nxt) > 3 and nxt[3])
     ws = [w for w in (w_post, w_next) if w is not None]
     for w in ws:
         _need(w, "add_rmsnorm weight", shape=(width,))
@@ -369,6 +397,13 @@ def add_rmsnorm(residual, branch, post, nxt, out_dtype, copy_out: bool = False):
         raise KernelError("add_rmsnorm: the two norms' weights differ in dtype; call the norms one by one")
     w_dt = _dt(ws[0], "add_rmsnorm weight") if ws else F32
     h = _fresh((rows, width), out_dtype, residual.device) if (w_next is not None or copy_out) else None
+    if center_post or center_next:
+        _check(
+            library().kb_add_norm(_ptr(residual), _ptr(src), b_dt, splits, ctypes.c_longlong(stride), _ptr(w_post), _f(eps_post),
+                                  _f(off_post), int(center_post), _ptr(w_next), _f(eps_next), _f(off_next), int(center_next),
+                                  _ptr(h), _CODES[out_dtype], w_dt, rows, width, _stream())
+        )
+        return h
     _check(
         library().kb_add_rmsnorm(_ptr(residual), _ptr(src), b_dt, splits, ctypes.c_longlong(stride), _ptr(w_post), _f(eps_post),
                                  _f(off_post), _ptr(w_next), _f(eps_next), _f(off_next), _ptr(h), _CODES[out_dtype], w_dt,
@@ -493,18 +528,26 @@ def attention_chunk() -> int:
 
 
 def paged_attention_rows(q, k_table, v_table, block_table, row_entry, row_count, page_size: int, window: Optional[int],
-                         scale: float, softcap: Optional[float], slots: int, keep_first: int = 0) -> torch.Tensor:
+                         scale: float, softcap: Optional[float], slots: int, keep_first: int = 0,
+                         sinks: Optional[torch.Tensor] = None, value_dim: Optional[int] = None) -> torch.Tensor:
     """Attention of each query row over its sequence's pages; `slots` is the largest number of
     key chunks (of `attention_chunk()` positions, cut at absolute multiples) any row touches, plus,
     with a window and `keep_first` > 0, the chunks of the first `keep_first` keys, which stay
-    visible below the window (`attention_keep_slots`). The values' size is the v table's last."""
+    visible below the window (`attention_keep_slots`). The values' size is the v table's last, or
+    `value_dim`: the first that many components of each of the v table's lines (the v table may then be
+    the k table itself). `sinks` [hq] float32: e^sink joins each row's denominator (no key, no value)."""
     rows, hq, d = q.shape
     _need(q, "attention q")
     _need(k_table, "attention k table", q.dtype)
     _need(v_table, "attention v table", q.dtype)
     if k_table.dim() != 4 or k_table.shape[2] != page_size or k_table.shape[3] != d or v_table.dim() != 4 or v_table.shape[:3] != k_table.shape[:3]:
         raise KernelError(f"attention: tables {tuple(k_table.shape)} / {tuple(v_table.shape)} are not [pages, kv_heads, {page_size}, {d}]")
-    n_pages, hkv, dv = k_table.shape[0], k_table.shape[1], v_table.shape[3]
+    n_pages, hkv, v_stride = k_table.shape[0], k_table.shape[1], v_table.shape[3]
+    dv = int(value_dim) if value_dim is not None else v_stride
+    if not 0 < dv <= v_stride:
+        raise KernelError(f"attention: values of {dv} in lines of {v_stride}")
+    if sinks is not None:
+        _need(sinks, "attention sinks", torch.float32, (hq,))
     _need(block_table, "attention block table", torch.int32)
     _need(row_entry, "attention row_entry", torch.int32, (rows,))
     _need(row_count, "attention row_count", torch.int32, (rows,))
@@ -516,7 +559,7 @@ def paged_attention_rows(q, k_table, v_table, block_table, row_entry, row_count,
         lib.kb_paged_attention_rows(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _dt(q, "attention q"), _ptr(block_table),
                                     _ptr(row_entry), _ptr(row_count), rows, hq, hkv, d, int(dv), int(page_size), int(block_table.shape[1]),
                                     int(n_pages), int(window or 0), int(keep_first or 0), int(slots), _f(scale), _f(softcap or 0.0),
-                                    _ptr(scratch), _stream())
+                                    _ptr(scratch), int(v_stride), _ptr(sinks), _stream())
     )
     return out
 
@@ -670,6 +713,9 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
 
 # ------------------------------------------------------------------------------------------
 # Mixers whose roles share one stacked product: a role is a run of columns of each row.
+GATE_ACTS = {"sigmoid": 0, "silu": 1}
+
+
 def _stacked(x, what: str):
     """(tensor, dtype code, slices, stride, rows, row width) of a stacked product (a tensor or a SplitSum)."""
     src, dt, splits, stride = _src(x, what)
@@ -713,10 +759,13 @@ def proj_norm_append(stacked, q_off: int, k_off: int, v_off: int, q_norm, k_norm
 
 
 def head_gate(y: torch.Tensor, stacked, g_off: int, weight: Optional[torch.Tensor], unit: bool, eps: float,
-              out_dtype: torch.dtype, pad_to: int = 0) -> torch.Tensor:
-    """y [rows, heads, e] times sigmoid of the columns g_off.. of `stacked`; with `unit` each head is
-    first divided by its root mean square (eps inside the root); `weight` [heads e] multiplies too.
+              out_dtype: torch.dtype, pad_to: int = 0, gate_act: str = "sigmoid") -> torch.Tensor:
+    """y [rows, heads, e] times sigmoid (or, with `gate_act` "silu", silu) of the columns g_off.. of
+    `stacked`; with `unit` each head is first divided by its root mean square (eps inside the
+    root); `weight` [heads e] multiplies too.
     The result is [rows, heads e], or [rows, pad_to] with zeros behind the heads."""
+    if gate_act not in GATE_ACTS:
+        raise KernelError(f"head_gate: gate activation {gate_act!r} is not known ({sorted(GATE_ACTS)})")
     _need(y, "head_gate input")
     rows, heads, e = y.shape
     src, dt, splits, stride, g_rows, width = _stacked(stacked, "head_gate gate")
@@ -729,7 +778,144 @@ def head_gate(y: torch.Tensor, stacked, g_off: int, weight: Optional[torch.Tenso
     _check(library().kb_head_gate(
         _ptr(out), _CODES[out_dtype], _ptr(y), _dt(y, "head_gate input"), _ptr(src), dt, splits, ctypes.c_longlong(stride), width,
         int(g_off), _ptr(weight), _dt(weight, "head_gate weight") if weight is not None else F32, int(bool(unit)), _f(eps),
-        ctypes.c_longlong(rows), heads, e, out_width, _stream()))
+        ctypes.c_longlong(rows), heads, e, out_width, GATE_ACTS[gate_act], _stream()))
+    return out
+
+
+def head_norm_rope_append(stacked, q_off: int, k_off: int, v_off: int, q_norm, k_norm, cos_sin, rotary: int, lines, k_table, v_table,
+                          hq: int, hkv: int, d: int, dv: int, write_kv: bool, out_dtype: torch.dtype) -> torch.Tensor:
+    """q [rows, hq, d] from the columns q_off.. of `stacked`: every head RMS-normed when `q_norm` =
+    (weight [d], eps, offset) is given (one weight for all heads), then its first `rotary` components
+    turned by `cos_sin` [rows, rotary/2, 2]; the keys likewise (`k_norm`) and the values as they are,
+    written at each row's line of the tables [pages, hkv, page_size, d] and [.., dv]."""
+    src, dt, splits, stride, rows, width = _stacked(stacked, "head_norm_rope_append input")
+    wq, eq, oq = q_norm[:3] if q_norm is not None else (None, 0.0, 0.0)
+    wk, ek, ok = k_norm[:3] if k_norm is not None else (None, 0.0, 0.0)
+    ws = [w for w in (wq, wk) if w is not None]
+    if len({w.dtype for w in ws}) > 1:
+        raise KernelError("head_norm_rope_append: the two norms' weights differ in dtype")
+    for w in ws:
+        _need(w, "head_norm_rope_append norm", shape=(d,))
+    w_dt = _dt(ws[0], "head_norm_rope_append norm") if ws else F32
+    if rotary:
+        _need(cos_sin, "head_norm_rope_append cos_sin", torch.float32, (rows, rotary // 2, 2))
+    q = _fresh((rows, hq, d), out_dtype, src.device)
+    table_lines, page_size = 0, 0
+    if write_kv:
+        _need(lines, "head_norm_rope_append lines", torch.int32, (rows,))
+        _need(k_table, "head_norm_rope_append k table", out_dtype)
+        _need(v_table, "head_norm_rope_append v table", out_dtype)
+        if k_table.dim() != 4 or k_table.shape[1] != hkv or k_table.shape[3] != d or v_table.dim() != 4 or \
+                tuple(v_table.shape) != (*k_table.shape[:3], dv):
+            raise KernelError(f"head_norm_rope_append: tables {tuple(k_table.shape)} / {tuple(v_table.shape)} are not [pages, {hkv}, page_size, {d} / {dv}]")
+        table_lines = k_table.shape[0] * k_table.shape[2]
+        page_size = k_table.shape[2]
+    _check(library().kb_head_norm_rope_append(
+        _ptr(src), dt, splits, ctypes.c_longlong(stride), width, int(q_off), int(k_off), int(v_off), _ptr(wq), _f(eq), _f(oq),
+        _ptr(wk), _f(ek), _f(ok), w_dt, _ptr(cos_sin if rotary else None), int(rotary), _ptr(lines if write_kv else None), _ptr(q),
+        _ptr(k_table if write_kv else None), _ptr(v_table if write_kv else None), _CODES[out_dtype], rows, hq, hkv, d, dv,
+        int(bool(write_kv)), ctypes.c_longlong(table_lines), int(page_size), _stream()))
+    return q
+
+
+def latent_append(stacked, q_off: int, kv_off: int, q_rank: int, kv_rank: int, rot: int, q_weight, kv_weight, eps: float, cos_sin,
+                  lines, k_table, write_kv: bool, out_dtype: torch.dtype, pad_to: int = 0) -> torch.Tensor:
+    """For attention through latents. Returns the query latent [rows, max(q_rank, pad_to)] (zeros
+    behind it): the columns q_off.. of `stacked`, RMS-normed with `q_weight`. The columns kv_off..
+    hold the key/value latent (kv_rank, RMS-normed with `kv_weight`) and the row's one rotated key
+    part (rot, turned by `cos_sin`); both are written, side by side, as the row's line of the table
+    [pages, 1, page_size, kv_rank + rot]."""
+    src, dt, splits, stride, rows, width = _stacked(stacked, "latent_append input")
+    _need(q_weight, "latent_append query norm", shape=(q_rank,))
+    _need(kv_weight, "latent_append key/value norm", q_weight.dtype, (kv_rank,))
+    if rot:
+        _need(cos_sin, "latent_append cos_sin", torch.float32, (rows, rot // 2, 2))
+    cq_width = max(int(pad_to), q_rank)
+    cq = _fresh((rows, cq_width), out_dtype, src.device)
+    table_lines, page_size = 0, 0
+    if write_kv:
+        _need(lines, "latent_append lines", torch.int32, (rows,))
+        _need(k_table, "latent_append table", out_dtype)
+        if k_table.dim() != 4 or k_table.shape[1] != 1 or k_table.shape[3] != kv_rank + rot:
+            raise KernelError(f"latent_append: a table of {tuple(k_table.shape)} is not [pages, 1, page_size, {kv_rank + rot}]")
+        table_lines = k_table.shape[0] * k_table.shape[2]
+        page_size = k_table.shape[2]
+    _check(library().kb_latent_append(
+        _ptr(src), dt, splits, ctypes.c_longlong(stride), width, int(q_off), int(kv_off), int(q_rank), int(kv_rank), int(rot),
+        _ptr(q_weight), _ptr(kv_weight), _dt(q_weight, "latent_append norm"), _f(eps), _ptr(cos_sin if rot else None),
+        _ptr(lines if write_kv else None), _ptr(cq), cq_width, _ptr(k_table if write_kv else None), _CODES[out_dtype], rows,
+        int(bool(write_kv)), ctypes.c_longlong(table_lines), int(page_size), _stream()))
+    return cq
+
+
+def head_linear(x, heads: int, x_head: int, x_off: int, m: torch.Tensor, y_head: Optional[int] = None, tail_off: int = 0,
+                tail: int = 0, cos_sin=None, gate=None, g_off: int = 0, pad_to: int = 0) -> torch.Tensor:
+    """y[r, h, :n_out] = x[r, h, x_off : x_off + n_in] . m[h] for `m` [heads, n_in, n_out] (its dtype is
+    the output's); `x` [rows, heads * x_head] is a tensor or a SplitSum. With `tail`, the components
+    x[r, h, tail_off : tail_off + tail] follow the product in y, turned by `cos_sin` [rows, tail/2, 2].
+    With `gate` (a float32 stacked product, tensor or SplitSum) the result is multiplied by the sigmoid
+    of its columns g_off + h * n_out ... The result is [rows, heads * y_head] (y_head defaults to
+    n_out + tail), or [rows, pad_to] with zeros behind the heads."""
+    src, x_dt, splits, stride, rows, x_row = _stacked(x, "head_linear input")
+    _need(m, "head_linear matrices")
+    if m.dim() != 3 or m.shape[0] != heads:
+        raise KernelError(f"head_linear: matrices of {tuple(m.shape)} for {heads} heads")
+    n_in, n_out = int(m.shape[1]), int(m.shape[2])
+    y_head = int(y_head) if y_head is not None else n_out + int(tail)
+    y_row = max(int(pad_to), heads * y_head)
+    if tail:
+        _need(cos_sin, "head_linear cos_sin", torch.float32, (rows, tail // 2, 2))
+    g_src, g_splits, g_stride, g_row = None, 1, 0, 0
+    if gate is not None:
+        g_src, g_dt, g_splits, g_stride, g_rows, g_row = _stacked(gate, "head_linear gate")
+        if g_dt != F32 or g_rows != rows:
+            raise KernelError("head_linear: the gate must be a float32 product of as many rows")
+    y = _fresh((rows, y_row), m.dtype, src.device)
+    _check(library().kb_head_linear(
+        _ptr(y), _dt(m, "head_linear matrices"), y_row, y_head, _ptr(src), x_dt, splits, ctypes.c_longlong(stride), x_row, int(x_head),
+        int(x_off), _ptr(m), n_in, n_out, rows, int(heads), int(tail_off), int(tail), _ptr(cos_sin if tail else None), _ptr(g_src),
+        int(g_splits), ctypes.c_longlong(g_stride), int(g_row), int(g_off), _stream()))
+    return y
+
+
+def delta_state_floats(heads: int, kv_heads: int, d: int, e: int, taps: int) -> int:
+    """Floats a request keeps between steps in a gated-delta-rule layer: the last taps - 1 inputs of
+    every convolved channel (queries, keys, values), then every head's memory [e, d]. Plain
+    arithmetic (a cache is sized without the CUDA library); `delta_scan` checks it against the library's."""
+    return (taps - 1) * (2 * kv_heads * d + heads * e) + heads * d * e
+
+
+def delta_scan(stacked, q_off: int, k_off: int, v_off: int, b_off: int, a_off: int, conv: torch.Tensor, a_log: torch.Tensor,
+               dt_bias: torch.Tensor, state: torch.Tensor, row_entry: torch.Tensor, ranges, slots, entries: int, heads: int,
+               kv_heads: int, d: int, e: int, taps: int, q_scale: float, unit_eps: float) -> torch.Tensor:
+    """The gated delta rule's read-out [rows, heads, e] (float32, not yet normed) over the rows of a
+    step, request by request in row order, from and into `state` [slots, state floats]. `conv`
+    [2 kv_heads d + heads e, taps] float32: the short convolutions' filters, the queries' channels
+    first, then the keys', then the values'."""
+    src, dt, splits, stride, rows, width = _stacked(stacked, "delta input")
+    channels = 2 * kv_heads * d + heads * e
+    _need(conv, "delta convolution filters", torch.float32, (channels, taps))
+    _need(a_log, "delta decay rates", torch.float32, (heads,))
+    _need(dt_bias, "delta step biases", torch.float32, (heads,))
+    _need(state, "delta state", torch.float32)
+    per = delta_state_floats(heads, kv_heads, d, e, taps)
+    lib = library()
+    if state.dim() != 2 or state.shape[1] != per or int(lib.kb_delta_state_floats(heads, kv_heads, d, e, taps)) != per:
+        raise KernelError(f"delta: a state table of {tuple(state.shape)}, expected [slots, {per}]")
+    start, end = ranges
+    _need(start, "delta entry starts", torch.int32)
+    _need(end, "delta entry ends", torch.int32)
+    _need(slots, "delta slots", torch.int32)
+    _need(row_entry, "delta row_entry", torch.int32, (rows,))
+    if min(start.numel(), end.numel(), slots.numel()) < entries:
+        raise KernelError(f"delta: {entries} requests but ranges or slots for fewer")
+    out = _fresh((rows, heads, e), torch.float32, src.device)
+    scratch = _fresh((max(1, int(lib.kb_delta_scratch_floats(rows, heads, kv_heads, d, e))),), torch.float32, src.device)
+    _check(lib.kb_delta_scan(
+        _ptr(out), _ptr(scratch), _ptr(src), dt, splits, ctypes.c_longlong(stride), width, int(q_off), int(k_off), int(v_off),
+        int(b_off), int(a_off), _ptr(conv), _ptr(a_log), _ptr(dt_bias), _ptr(state), int(state.shape[0]), ctypes.c_longlong(per),
+        _ptr(row_entry), _ptr(start), _ptr(end), _ptr(slots), int(entries), rows, heads, kv_heads, d, e, int(taps), _f(q_scale),
+        _f(unit_eps), _stream()))
     return out
 
 

@@ -3,11 +3,14 @@ from .attention import Attention
 from .base import (BuildContext, LayerCache, Part, linear, matrix_for, matrix_named, pad_columns, product_width,
                    require_product_widths, stack_rows)
 from .block import PostNormBlock, PreNormBlock, SandwichBlock
+from .delta import Delta
 from .embedding import Embedding, VocabHead
 from .feed_forward import GatedMLP
+from .input_mix import InputMix
+from .latent_attention import LatentAttention
 from .mlstm import MLSTM
 from .moe import MoE
-from .norm import RMSNorm, add_branch
+from .norm import LayerNorm, RMSNorm, add_branch
 from .position import NoPosition, Rope
 from .registry import (
     build_part,
@@ -23,9 +26,13 @@ from .registry import (
 
 register_part("mixer", "attention", Attention)
 register_part("mixer", "mlstm", MLSTM)
+register_part("mixer", "latent_attention", LatentAttention)
+register_part("mixer", "delta", Delta)
+register_part("merge", "input_mix", InputMix)
 register_part("feed_forward", "gated_mlp", GatedMLP)
 register_part("feed_forward", "moe", MoE)
 register_part("norm", "rms", RMSNorm)
+register_part("norm", "layer", LayerNorm)
 register_part("position", "rope", Rope)
 register_part("position", "none", NoPosition)
 register_part("block", "sandwich", SandwichBlock)
@@ -43,4 +50,7 @@ def expected_tensors(spec) -> dict:
     out.update(part_class("norm", n.kind).expected_tensors(n))
     for layer in spec.layers:
         out.update(part_class("block", layer.kind).expected_tensors(layer))
+    for e in spec.schedule:
+        if getattr(e, "before", None) is not None:
+            out.update(part_class("merge", e.before.kind).expected_tensors(e.before))
     return out

@@ -11,6 +11,11 @@ another size than keys, first keys that stay visible below the window, a sigmoid
 heads' outputs. Such a layer runs the general path: one stacked product q|k|v|g in 32-bit, one
 kernel that norms q and k and appends k and v to the cache, the row-wise attention kernel (which
 knows the kept first keys and the values' size), the gate, the output product.
+
+A spec with an RMS norm over every head's query and key (`q_head_norm`, `k_head_norm`: one weight
+of the head's size for all heads) runs the third path: the stacked product in 32-bit, one kernel
+that norms each head, rotates it and appends keys and values (of their own size) to the cache,
+then the tensor-core kernels where keys and values have one size and the row-wise kernel elsewhere.
 """
 from __future__ import annotations
 
@@ -34,7 +39,7 @@ class Attention(Part):
                w["o"]: (spec.hidden, spec.num_heads * dv)}
         if spec.gated:
             out[w["g"]] = (spec.num_heads * dv, spec.hidden)
-        for n in (spec.q_norm, spec.k_norm):
+        for n in (spec.q_norm, spec.k_norm, spec.q_head_norm, spec.k_head_norm):
             if n is not None:
                 out[n.weight] = (n.width,)
         return out
@@ -44,7 +49,13 @@ class Attention(Part):
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError(f"attention: {spec.num_heads} heads over {spec.num_kv_heads} kv heads")
         self.v_dim = spec.v_head_dim or spec.head_dim
-        self.general = bool(spec.gated or spec.q_norm or spec.k_norm or spec.keep_first or self.v_dim != spec.head_dim)
+        self.by_head = bool(spec.q_head_norm or spec.k_head_norm)
+        self.general = bool(spec.gated or spec.q_norm or spec.k_norm or spec.keep_first or self.v_dim != spec.head_dim) and not self.by_head
+        if self.by_head and (spec.q_norm or spec.k_norm or spec.keep_first or spec.window):
+            raise ValueError("attention: norms over each head together with norms over the whole projection, a window or kept first keys are not built")
+        for n in (spec.q_head_norm, spec.k_head_norm):
+            if n is not None and (n.kind != "rms" or n.width != spec.head_dim):
+                raise ValueError(f"attention: a norm over each head must be an RMS norm of width {spec.head_dim}")
         if not self.general and spec.head_dim % 16:
             raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16 for the kernels")
         if spec.keep_first < 0 or (spec.keep_first and not spec.window):
@@ -52,7 +63,7 @@ class Attention(Part):
         for n, width in ((spec.q_norm, spec.num_heads * spec.head_dim), (spec.k_norm, spec.num_kv_heads * spec.head_dim)):
             if n is not None and (n.kind != "rms" or n.width != width):
                 raise ValueError(f"attention: a norm over the whole projection must be an RMS norm of width {width}")
-        if not self.general:
+        if not self.general and not self.by_head:
             require_product_widths(ctx, "attention", hidden_size=spec.hidden,
                                    **{"num_attention_heads x value size": spec.num_heads * self.v_dim})
         self.position = build_part("position", spec.position, ctx)
@@ -64,10 +75,10 @@ class Attention(Part):
         names = [w["q"], w["k"], w["v"]] + ([w["g"]] if self.spec.gated else [])
         self.w_qkv = stack_rows(self.ctx, tensors, names, "attention")
         self.w_o = matrix_named(self.ctx, tensors, w["o"])
-        if self.general and self.spec.gated:
+        if (self.general and self.spec.gated) or self.by_head:
             self.w_o = pad_columns(self.ctx, self.w_o)
         self.proj_norms = []
-        for n in (self.spec.q_norm, self.spec.k_norm):
+        for n in (self.spec.q_head_norm, self.spec.k_head_norm) if self.by_head else (self.spec.q_norm, self.spec.k_norm):
             if n is None:
                 self.proj_norms.append(None)
                 continue
@@ -109,8 +120,39 @@ class Attention(Part):
             return linear(self.ctx, y, self.w_o, keep_split=True)
         return linear(self.ctx, y.view(y.shape[0], s.num_heads * dv), self.w_o, keep_split=True)
 
+    def forward_by_head(self, h, batch, cache):
+        s, dv = self.spec, self.v_dim
+        nq, nk = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        stacked = linear(self.ctx, h, self.w_qkv, out_dtype=torch.float32, keep_split=True)
+        k_table, v_table = cache.tables()
+        group = batch.groups[cache.group]
+        rotary = self.position.rotary_dim
+        q = K.head_norm_rope_append(stacked, 0, nq, nq + nk, self.proj_norms[0], self.proj_norms[1],
+                                    self.position.tables(batch) if rotary else None, rotary, group.lines, k_table, v_table,
+                                    s.num_heads, s.num_kv_heads, s.head_dim, dv, cache.owns, self.ctx.dtype)
+        heads_per_kv = s.num_heads // s.num_kv_heads
+        if dv == s.head_dim and s.head_dim % 16 == 0 and K.attention_mma_takes(q.dtype, s.head_dim, heads_per_kv):
+            decode, tiles, split, slots, relative = batch.attention_tiles(
+                heads_per_kv, s.num_kv_heads, None, s.head_dim,
+                K.attention_prompt_kernel(s.num_heads, s.num_kv_heads, s.head_dim, self.ctx.page_size, s.softcap))
+            y = K.paged_attention_mma(q, k_table, v_table, group.block_table, batch.row_count, tiles, self.ctx.page_size, None,
+                                      s.scale, s.softcap, decode, split, slots, relative, pairs=getattr(batch, "pairs", None))
+        else:
+            y = K.paged_attention_rows(q, k_table, v_table, group.block_table, batch.row_entry, batch.row_count, self.ctx.page_size,
+                                       None, s.scale, s.softcap, batch.attention_slots(None))
+        width = product_width(self.ctx, s.num_heads * dv)
+        if s.gated:
+            y = K.head_gate(y, stacked, nq + nk + s.num_kv_heads * dv, None, False, 0.0, self.ctx.dtype, pad_to=width)
+        else:
+            y = y.view(y.shape[0], s.num_heads * dv)
+            if width != y.shape[1]:
+                y = K.pad_cols(y, width)
+        return linear(self.ctx, y, self.w_o, keep_split=True)
+
     def forward(self, h, batch, cache):
         s = self.spec
+        if self.by_head:
+            return self.forward_by_head(h, batch, cache)
         if self.general:
             return self.forward_general(h, batch, cache)
         qkv = linear(self.ctx, h, self.w_qkv, keep_split=True)

@@ -2,6 +2,7 @@
 
 "sandwich" (Gemma 2; crates/kapel-models/src/model.rs:1401-1460):
     h = pre_mixer(x); a = mixer(h); x += post_mixer(a); h = pre_ffn(x); m = ffn(h); x += post_ffn(m)
+    (a layer without a feed-forward ends after the first sum)
 "prenorm": the same without the post norms.
 "postnorm": the branches read the residual itself (rounded to the activation dtype), and only their
     outputs are normed: x += post_mixer(mixer(x)); x += post_ffn(ffn(x)); a layer may have no
@@ -22,29 +23,37 @@ class SandwichBlock(Part):
     norm_roles = ("pre_mixer", "post_mixer", "pre_ffn", "post_ffn")
 
     @classmethod
+    def roles_of(cls, spec):
+        """The norms a layer of this arrangement has: without a feed-forward, those around the mixer."""
+        return cls.norm_roles if spec.ffn is not None else tuple(r for r in cls.norm_roles if r.endswith("_mixer"))
+
+    @classmethod
     def expected_tensors(cls, spec):
         from .registry import part_class
 
         out = {}
         out.update(part_class("mixer", spec.mixer.kind).expected_tensors(spec.mixer))
-        out.update(part_class("feed_forward", spec.ffn.kind).expected_tensors(spec.ffn))
-        for role in cls.norm_roles:
+        if spec.ffn is not None:
+            out.update(part_class("feed_forward", spec.ffn.kind).expected_tensors(spec.ffn))
+        for role in cls.roles_of(spec):
             n = spec.norms[role]
             out.update(part_class("norm", n.kind).expected_tensors(n))
         return out
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
-        missing = [r for r in self.norm_roles if r not in spec.norms]
+        roles = self.roles_of(spec)
+        missing = [r for r in roles if r not in spec.norms]
         if missing:
             raise ValueError(f"{spec.kind} block: norms {missing} are missing")
         self.mixer = build_part("mixer", spec.mixer, ctx)
-        self.ffn = build_part("feed_forward", spec.ffn, ctx)
-        self.norms = {r: build_part("norm", spec.norms[r], ctx) for r in self.norm_roles}
+        self.ffn = build_part("feed_forward", spec.ffn, ctx) if spec.ffn is not None else None
+        self.norms = {r: build_part("norm", spec.norms[r], ctx) for r in roles}
 
     @property
     def graph_safe(self) -> bool:
-        return all(p.graph_safe for p in (self.mixer, self.ffn, *self.norms.values()))
+        parts = [self.mixer, *self.norms.values()] + ([self.ffn] if self.ffn is not None else [])
+        return all(p.graph_safe for p in parts)
 
     def cache_needs(self):
         """What this layer keeps between steps: its mixer's pages and state."""
@@ -57,7 +66,8 @@ class SandwichBlock(Part):
 
     def load(self, tensors):
         self.mixer.load(tensors)
-        self.ffn.load(tensors)
+        if self.ffn is not None:
+            self.ffn.load(tensors)
         for n in self.norms.values():
             n.load(tensors)
 
@@ -65,6 +75,8 @@ class SandwichBlock(Part):
         if h is None:
             h = self.norms["pre_mixer"].forward(x)
         a = self.mixer.forward(h, batch, cache)
+        if self.ffn is None:
+            return x, add_branch(self.ctx, x, a, self.norms.get("post_mixer"), next_norm)
         h = add_branch(self.ctx, x, a, self.norms.get("post_mixer"), self.norms["pre_ffn"])
         m = self.ffn.forward(h)
         h_next = add_branch(self.ctx, x, m, self.norms.get("post_ffn"), next_norm)

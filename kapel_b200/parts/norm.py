@@ -27,6 +27,18 @@ class RMSNorm(Part):
         return (self.weight, self.spec.eps, self.spec.offset)
 
 
+class LayerNorm(RMSNorm):
+    """y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * (offset + w): a layer norm with a weight and
+    no bias, in 32-bit. The fused sum-and-norm kernel takes it by a flag beside the RMS norm's triple."""
+
+    def forward(self, x, out_dtype=None):
+        return K.layernorm(x, self.weight, self.spec.eps, self.spec.offset, out_dtype or self.ctx.dtype)
+
+    def fuse_key(self):
+        """(weight, eps, offset, True): the last says that the row's mean is taken off first."""
+        return (self.weight, self.spec.eps, self.spec.offset, True)
+
+
 def add_branch(ctx, residual, branch, post_norm, next_norm, copy_out: bool = False):
     """residual += post_norm(branch) (post_norm None: plain sum); returns next_norm(residual),
     or None without a next norm (with `copy_out`: the new residual in the activation dtype, for a

@@ -1,6 +1,6 @@
 """Position encodings. A mixer owns one and asks it for what its kernels take.
 
-kind "rope": theta^(-2j/r) frequencies, pairing (j, j + r/2), all in one table of (cos, sin)
+kind "rope": theta^(-2j/r) frequencies (each divided by the spec's `divisor`), pairing (j, j + r/2), all in one table of (cos, sin)
 per row made once a step with angles in 64-bit (crates/kapel-ops/src/rope.rs:63-101;
 kernels/src/lib.rs rope_table :1092). kind "none": no rotation.
 """
@@ -19,6 +19,8 @@ class Rope(Part):
             raise ValueError(f"rope pairing {spec.pairing!r} is not built (only \"half\")")
         if spec.rotary_dim <= 0 or spec.rotary_dim % 2:
             raise ValueError(f"rope rotary_dim {spec.rotary_dim} must be positive and even")
+        if not getattr(spec, "divisor", 1.0) > 0:
+            raise ValueError(f"rope divisor {spec.divisor} must be positive")
 
     @property
     def rotary_dim(self) -> int:
@@ -27,9 +29,10 @@ class Rope(Part):
     def tables(self, batch):
         """(cos, sin) [rows, rotary/2, 2] for this step's positions; shared by every layer with
         the same theta and rotary width."""
-        key = ("rope", float(self.spec.theta), int(self.spec.rotary_dim))
+        divisor = float(getattr(self.spec, "divisor", 1.0))
+        key = ("rope", float(self.spec.theta), int(self.spec.rotary_dim), divisor)
         if key not in batch.memo:
-            batch.memo[key] = K.rope_table(batch.positions, self.spec.rotary_dim, self.spec.theta)
+            batch.memo[key] = K.rope_table(batch.positions, self.spec.rotary_dim, self.spec.theta, divisor)
         return batch.memo[key]
 
 

@@ -1,6 +1,6 @@
 """Which class builds which part: one table per category, keyed by a spec's `kind`.
 
-Categories: "mixer", "feed_forward", "norm", "position", "block", "embedding", "head". A new
+Categories: "mixer", "feed_forward", "norm", "position", "block", "merge", "embedding", "head". A new
 part registers its class under a new kind; a configuration that names that kind in its
 ModelSpec gets it built, with no change to the engine. The interface each class must have is
 in `kapel_b200.parts.base`.
@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from typing import Dict, Tuple
 
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "merge", "embedding", "head")
 _PARTS: Dict[Tuple[str, str], type] = {}
 
 

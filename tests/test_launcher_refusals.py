@@ -21,7 +21,7 @@ def lib():
     lib.kb_gemm_tcgen05.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, f32, i32, vp]
     lib.kb_gemm_skinny.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32, i32, f32, vp]
     lib.kb_gemm_f32.argtypes = [vp, vp, vp, i32, i32, i32, i32, f32, vp]
-    lib.kb_rope_table.argtypes = [vp, vp, i32, i32, f64, vp]
+    lib.kb_rope_table.argtypes = [vp, vp, i32, i32, f64, f64, vp]
     lib.kb_rope_append.argtypes = [vp, i32, i32, i64, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, i32, vp]
     lib.kb_glu.argtypes = [vp, i32, vp, i32, i32, i64, i64, i32, i32, vp]
     lib.kb_attention_tc.argtypes = [vp] * 9 + [i32] * 11 + [f32, f32, vp, i32, vp]
@@ -56,8 +56,9 @@ def test_products_refuse_rows_that_are_no_multiple_of_16_bytes_and_unknown_choic
 
 
 def test_rotation_refuses_odd_sizes(lib):
-    refused(lib, lib.kb_rope_table(A, A, 4, 7, 10000.0, None), "rope_table", "rotary 7 (must be even)")
-    refused(lib, lib.kb_rope_table(A, A, 4, 8, 0.0, None), "theta 0 must be positive")
+    refused(lib, lib.kb_rope_table(A, A, 4, 7, 10000.0, 1.0, None), "rope_table", "rotary 7 (must be even)")
+    refused(lib, lib.kb_rope_table(A, A, 4, 8, 0.0, 1.0, None), "theta 0 must be positive")
+    refused(lib, lib.kb_rope_table(A, A, 4, 8, 10000.0, 0.0, None), "divisor 0 must be positive")
     refused(lib, lib.kb_rope_append(A, BF16, 1, 0, A, A, A, A, A, BF16, 4, 2, 1, 15, 14, 1, 64, 16, None), "rope_append", "head_dim 15")
     refused(lib, lib.kb_rope_append(A, BF16, 1, 0, A, A, A, A, A, BF16, 4, 2, 1, 16, 18, 1, 64, 16, None), "rotary 18", "at most head_dim 16")
     refused(lib, lib.kb_rope_append(A, BF16, 0, 0, A, A, A, A, A, BF16, 4, 2, 1, 16, 16, 1, 64, 16, None), "0 slices")
