@@ -372,9 +372,11 @@ static int dispatch_lanes(const AttParams& p, cudaStream_t s) {
         }
     } else if (vpl <= 4 && lpk == 32) {
         KB_ATT(32, 4);
+    } else if (vpl <= 8 && lpk == 32) {
+        KB_ATT(32, 8);
     }
 #undef KB_ATT
-    return fail("paged_attention: head_dim %d is not handled (at most %d)", p.d, 32 * 4 * Vec<T>::N);
+    return fail("paged_attention: head_dim %d is not handled (at most %d)", p.d, 32 * 8 * Vec<T>::N);
 }
 
 template <typename T>

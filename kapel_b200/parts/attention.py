@@ -56,7 +56,7 @@ class Attention(Part):
         for n in (spec.q_head_norm, spec.k_head_norm):
             if n is not None and (n.kind != "rms" or n.width != spec.head_dim):
                 raise ValueError(f"attention: a norm over each head must be an RMS norm of width {spec.head_dim}")
-        if not self.general and spec.head_dim % 16:
+        if not self.general and not self.by_head and spec.head_dim % 16:
             raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16 for the kernels")
         if spec.keep_first < 0 or (spec.keep_first and not spec.window):
             raise ValueError(f"attention: {spec.keep_first} first keys kept with window {spec.window}")

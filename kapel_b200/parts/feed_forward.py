@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels as K
-from .base import Part, linear, matrix_named, require_product_widths, stack_rows
+from .base import Part, linear, matrix_named, stack_rows
 
 
 class GatedMLP(Part):
@@ -24,7 +24,8 @@ class GatedMLP(Part):
         super().__init__(spec, ctx)
         if spec.activation not in K.ACT_CODES:
             raise ValueError(f"gated_mlp: activation {spec.activation!r} is not built")
-        require_product_widths(ctx, "gated_mlp", hidden_size=spec.hidden, intermediate_size=spec.intermediate)
+        # widths that are no multiple of 8 go through the products that pad their rows (`linear`), unfused
+        self.fusable = spec.hidden % 8 == 0 and spec.intermediate % 8 == 0
 
     def load(self, tensors):
         w = self.spec.weights
@@ -33,7 +34,7 @@ class GatedMLP(Part):
 
     def forward(self, h):
         # many rows of bfloat16: the gated unit is the epilogue of the gate|up product
-        inner = K.gemm_glu_fused(h, self.w_gate_up, self.spec.activation) if h.dtype == self.w_gate_up.dtype else None
+        inner = K.gemm_glu_fused(h, self.w_gate_up, self.spec.activation) if (self.fusable and h.dtype == self.w_gate_up.dtype) else None
         if inner is None:
             gu = linear(self.ctx, h, self.w_gate_up, keep_split=True)
             inner = K.glu(gu, self.spec.activation, out_dtype=self.ctx.dtype)

@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels as K
-from .base import Part, linear, matrix_named, require_product_widths
+from .base import Part, linear, matrix_named
 
 
 class InputMix(Part):
@@ -18,10 +18,6 @@ class InputMix(Part):
     @staticmethod
     def expected_tensors(spec):
         return {spec.weight: (spec.hidden, 2 * spec.hidden)}
-
-    def __init__(self, spec, ctx):
-        super().__init__(spec, ctx)
-        require_product_widths(ctx, "input_mix", **{"2 x width": 2 * spec.hidden})
 
     def load(self, tensors):
         self.weight = matrix_named(self.ctx, tensors, self.spec.weight)

@@ -125,27 +125,47 @@ def short_conv(x, w):
     return y
 
 
+def delta_recurrence(q, k, v, g, beta):
+    """One head. q, k [T, d], v [T, e], g, beta [T]: per row S <- g S; u = beta (v - S^T k);
+    S <- S + k u^T; o = S^T q, so the read-out sees the row's own write. Returns o [T, e]."""
+    T, d = k.shape
+    S = np.zeros((d, v.shape[1]), dtype=v.dtype)
+    out = np.zeros_like(v)
+    for i in range(T):
+        S = g[i] * S
+        u = beta[i] * (v[i] - S.T @ k[i])
+        S = S + np.outer(k[i], u)
+        out[i] = S.T @ q[i]
+    return out
+
+
+def unit(x, eps=1e-6):
+    return x / np.sqrt((x * x).sum(axis=-1, keepdims=True) + eps)
+
+
+def delta_inputs(x, conv, a_log, dt_bias, H, G, d, e):
+    """From the stacked projections x [T, 2 G d + H e + 2 H] (q | k | v | b | a) and the filters
+    conv [2 G d + H e, taps]: unit q (times d^-1/2) and k [T, G, d], v [T, H, e], decay and step size [T, H]."""
+    T = x.shape[0]
+    n = G * d
+    y = silu(short_conv(x[:, : 2 * n + H * e], conv))
+    q = unit(y[:, :n].reshape(T, G, d)) * d ** -0.5
+    k = unit(y[:, n : 2 * n].reshape(T, G, d))
+    v = y[:, 2 * n :].reshape(T, H, e)
+    beta = sigmoid(x[:, 2 * n + H * e : 2 * n + H * e + H])
+    g = np.exp(-np.exp(a_log) * softplus(x[:, 2 * n + H * e + H :] + dt_bias))
+    return q, k, v, g, beta
+
+
 def delta_mixer(h, t, prefix, m, eps):
-    """The gated delta rule. Per head a memory S [d, e]: S <- g S; u = beta (v - S^T k); S <- S + k u^T;
-    read-out S^T q, which sees the row's own write."""
+    """The gated delta rule behind short convolutions; each head's read-out is divided by its root mean
+    square, times a weight shared by the heads, times silu of a gate."""
     H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
-    q = silu(short_conv(h @ t[f"{prefix}.q"].T, t[f"{prefix}.q.conv"])).reshape(T, G, d)
-    k = silu(short_conv(h @ t[f"{prefix}.k"].T, t[f"{prefix}.k.conv"])).reshape(T, G, d)
-    v = silu(short_conv(h @ t[f"{prefix}.v"].T, t[f"{prefix}.v.conv"])).reshape(T, H, e)
-    q = q / np.sqrt((q * q).sum(axis=-1, keepdims=True) + 1e-6) * d ** -0.5
-    k = k / np.sqrt((k * k).sum(axis=-1, keepdims=True) + 1e-6)
-    beta = sigmoid(h @ t[f"{prefix}.b"].T)                                          # [T, H]
-    g = np.exp(-np.exp(t[f"{prefix}.A_log"]) * softplus(h @ t[f"{prefix}.a"].T + t[f"{prefix}.dt_bias"]))
-    out = np.zeros((T, H, e), dtype=h.dtype)
-    for a in range(H):
-        kv = a // (H // G)
-        S = np.zeros((d, e), dtype=h.dtype)
-        for i in range(T):
-            S = g[i, a] * S
-            u = beta[i, a] * (v[i, a] - S.T @ k[i, kv])
-            S = S + np.outer(k[i, kv], u)
-            out[i, a] = S.T @ q[i, kv]
+    x = np.concatenate([h @ t[f"{prefix}.{r}"].T for r in ("q", "k", "v", "b", "a")], axis=1)
+    conv = np.concatenate([t[f"{prefix}.{r}.conv"] for r in ("q", "k", "v")], axis=0)
+    q, k, v, g, beta = delta_inputs(x, conv, t[f"{prefix}.A_log"], t[f"{prefix}.dt_bias"], H, G, d, e)
+    out = np.stack([delta_recurrence(q[:, a // (H // G)], k[:, a // (H // G)], v[:, a], g[:, a], beta[:, a]) for a in range(H)], axis=1)
     out = rms_unit(out, eps) * t[f"{prefix}.norm"]
     gate = silu(h @ t[f"{prefix}.g"].T).reshape(T, H, e)
     return (out * gate).reshape(T, H * e) @ t[f"{prefix}.o"].T

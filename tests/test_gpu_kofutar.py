@@ -1,0 +1,638 @@
+"""Kofutar on the GPU: each mechanism's kernels against the plain functions of `plain_kofutar`, and
+the engine (step function, cache, scheduler, entry point) against the plain forward pass, on small
+configurations that differ in every size, constant and in the order of their layers."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import plain_kofutar as PK
+from helpers import TraceBuilder, random_tokens, rel_err, run_trace_engine
+
+pytestmark = pytest.mark.gpu
+
+
+def attention_layer(heads, kv_heads, dim, vdim, scale, rot, ff):
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if rot is not None:
+        mixer["rot"] = rot
+    return {"type": "attention", "mixer": mixer, "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def latent_layer(heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, base, ff, factor=None):
+    rot = {"base": base, "dims": rot_dim}
+    if factor is not None:
+        rot["scaling"] = {"factor": factor}
+    return {"type": "latent_attention", "mlp": None if ff is None else {"kind": "dense", "ff": ff},
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": scale, "rot": rot}}
+
+
+def delta_layer(heads, kv_heads, dim, vdim, conv, ff):
+    return {"type": "delta", "mlp": None if ff is None else {"kind": "dense", "ff": ff},
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}}
+
+
+# A: the loop covers the middle layers and runs three times; a delta layer first; values wider and narrower
+# than keys; a layer without a feed-forward; a rotation of part of the head with stretched positions.
+# B: no loop key at all; one head, one key head, a convolution of one tap (no history), the whole head rotated.
+# C: the loop is the whole model, once; latents wider than the heads' sizes.
+KOFUTAR_A = {"architecture": "Kofutar", "vocab": 131, "width": 64, "norm": {"eps": 1e-5}, "loop": {"start": 1, "stop": 3, "times": 3}, "layers": [
+    delta_layer(4, 2, 16, 24, 3, 48),
+    attention_layer(6, 2, 16, 8, 0.3, {"base": 5000.0, "dims": 8, "scaling": {"factor": 4.0}}, None),
+    latent_layer(3, 8, 4, 16, 24, 12, 0.2, 100.0, 40),
+    delta_layer(2, 2, 40, 8, 4, 32),
+]}
+KOFUTAR_B = {"architecture": "Kofutar", "vocab": 89, "width": 48, "norm": {"eps": 1e-6}, "layers": [
+    attention_layer(1, 1, 32, 32, 0.18, {"base": 300.0, "dims": 32}, 24),
+    delta_layer(1, 1, 24, 20, 1, None),
+    latent_layer(1, 16, 16, 8, 8, 40, 0.25, 10000.0, 56, factor=2.0),
+]}
+KOFUTAR_C = {"architecture": "Kofutar", "vocab": 64, "width": 32, "norm": {"eps": 1e-5}, "loop": {"start": 0, "stop": 2, "times": 1}, "layers": [
+    latent_layer(4, 8, 8, 8, 48, 32, 0.35, 20.0, 32),
+    attention_layer(4, 4, 8, 16, 0.35, None, 16),
+]}
+CONFIGS = {"A": (KOFUTAR_A, 21), "B": (KOFUTAR_B, 22), "C": (KOFUTAR_C, 23)}
+# Largest difference of logits over the largest plain logit, row by row. The 32-bit runs see about 1e-5 and every row
+# is held to 1e-4. In bfloat16 (products and caches in bfloat16 under 32-bit norms, scores and recurrences) the median
+# row of these small models sees 5e-3 to 1e-2; a few rows see ten times that where a random layer happens to magnify
+# what it is given (the 32-bit run shows the same rows ten times above its median). So a bfloat16 run is held to: the
+# median row under 3e-2, at most one row in fifty over 1e-1, none over 3e-1. A wrong key, a lost state or a
+# forgotten sink moves every row by tenths.
+TOL = {"float32": 1e-4, "bfloat16": 3e-1}
+
+
+def check_rows(results, builder, plain_by_request, dtype, what=""):
+    errs = []
+    for step, rows in builder.rows.items():
+        assert step in results, f"{what}: step {step} wrote no logits"
+        got = results[step]
+        assert got.shape[0] == len(rows), f"{what}: step {step}: {got.shape[0]} rows for {len(rows)} wanted"
+        for i, (rid, pos) in enumerate(rows):
+            err = rel_err(got[i], plain_by_request[rid][pos])
+            assert err <= TOL[dtype], f"{what}: step {step}, request {rid}, position {pos}: relative error {err:.3e} > {TOL[dtype]:.1e}"
+            errs.append(err)
+    errs = np.asarray(errs)
+    if dtype == "bfloat16":
+        assert np.median(errs) < 3e-2 and (errs > 1e-1).sum() <= max(1, len(errs) // 50), f"{what}: median {np.median(errs):.2e}, {(errs > 1e-1).sum()} of {len(errs)} rows over 1e-1"
+    return float(errs.max())
+
+
+def make_folder(raw, seed, tmp):
+    from kapel_b200.config import config_from_json
+    from kapel_b200.weights import write_random_model
+
+    return write_random_model(tmp, config_from_json(raw), seed)
+
+
+def read_tensors(folder):
+    """{name: float64 array} of a folder's model.safetensors, read with this file's own few lines."""
+    blob = (folder / "model.safetensors").read_bytes()
+    n = int.from_bytes(blob[:8], "little")
+    header = json.loads(blob[8 : 8 + n])
+    out = {}
+    for name, rec in header.items():
+        if name == "__metadata__":
+            continue
+        a, b = rec["data_offsets"]
+        raw = np.frombuffer(blob[8 + n + a : 8 + n + b], dtype="<u2" if rec["dtype"] == "BF16" else "<f4")
+        if rec["dtype"] == "BF16":
+            raw = (raw.astype(np.uint32) << 16).view(np.float32)
+        out[name] = raw.reshape(rec["shape"]).astype(np.float64)
+    return out
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for name, (raw, seed) in CONFIGS.items():
+        folder = make_folder(raw, seed, tmp_path_factory.mktemp(f"kofutar_{name}"))
+        out[name] = (folder, raw, read_tensors(folder))
+    return out
+
+
+_PLAIN = {}
+
+
+def plain(models, name, tokens):
+    key = (name, tuple(tokens))
+    if key not in _PLAIN:
+        _, raw, t = models[name]
+        _PLAIN[key] = PK.forward(raw, t, list(tokens))
+    return _PLAIN[key]
+
+
+def dev(a, dtype=torch.float32):
+    return torch.tensor(np.asarray(a), dtype=dtype, device="cuda").contiguous()
+
+
+def bf16_round(a):
+    return torch.tensor(np.asarray(a), dtype=torch.bfloat16).double().numpy()
+
+
+# -------------------------------------------------------------------------------------- kernels alone
+@pytest.mark.parametrize("width", [40, 52, 320, 9000])
+def test_layer_norm_alone_and_fused_with_the_sum(width):
+    """The centered norm; residual += norm(branch) and the next norm of the sum in one kernel, with either
+    norm centered or not, a branch that is split-K partial sums, an output without a next norm."""
+    from kapel_b200 import kernels as K
+
+    rng = np.random.default_rng(width)
+    rows = 5
+    x = rng.standard_normal((rows, width)) * 3 + 1.5
+    b = rng.standard_normal((rows, width)) * 0.2 - 4.0                              # a mean far from zero: forgetting to take it off shows
+    w1, w2 = rng.standard_normal(width), rng.standard_normal(width)
+    got = K.layernorm(dev(x), dev(w1), 1e-5, 0.0, torch.float32).cpu().numpy()
+    assert rel_err(got, PK.layer_norm(x, w1, 1e-5)) < 2e-6
+    parts = rng.standard_normal((3, rows, width))
+    parts[2] = b - parts[0] - parts[1]
+    for post_c, next_c in ((True, True), (True, False), (False, True)):
+        for branch in (dev(b), K.SplitSum(dev(parts))):
+            res = dev(x)
+            post = (dev(w1), 1e-5, 0.0, post_c)
+            nxt = (dev(w2), 1e-6, 0.0, next_c)
+            h = K.add_rmsnorm(res, branch, post, nxt, torch.float32)
+            normed = PK.layer_norm(b, w1, 1e-5) if post_c else PK.rms_unit(b, 1e-5) * w1
+            want_res = x + normed
+            want_h = PK.layer_norm(want_res, w2, 1e-6) if next_c else PK.rms_unit(want_res, 1e-6) * w2
+            assert rel_err(res.cpu().numpy(), want_res) < 1e-5 and rel_err(h.cpu().numpy(), want_h) < 1e-5
+    res = dev(x)
+    copy = K.add_rmsnorm(res, dev(b), (dev(w1), 1e-5, 0.0, True), None, torch.float32, copy_out=True)
+    assert torch.equal(copy, res) and rel_err(res.cpu().numpy(), x + PK.layer_norm(b, w1, 1e-5)) < 1e-5
+
+
+def test_rotation_table_with_stretched_positions():
+    from kapel_b200 import kernels as K
+
+    pos = np.array([0, 1, 17, 1000, 70000])
+    got = K.rope_table(dev(pos, torch.int32), 12, 5000.0, 4.0).cpu().numpy()
+    x = np.zeros((len(pos), 1, 12))
+    x[..., :6] = 1.0                                                                 # (1, 0) pairs turn into (cos, sin)
+    turned = PK.rotate(x, pos, {"base": 5000.0, "dims": 12, "scaling": {"factor": 4.0}})
+    assert np.abs(got[..., 0] - turned[:, 0, :6]).max() < 1e-6 and np.abs(got[..., 1] - turned[:, 0, 6:]).max() < 1e-6
+
+
+def paged(rng, n_tokens, page_size=16, spare=3):
+    """A shuffled block table for one request of n_tokens positions and its lines."""
+    n_pages = -(-n_tokens // page_size)
+    pages = rng.permutation(n_pages + spare)[:n_pages]
+    lines = np.array([pages[p // page_size] * page_size + p % page_size for p in range(n_tokens)])
+    return n_pages + spare, pages, lines
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 5e-6), (torch.bfloat16, 1.5e-2)])
+@pytest.mark.parametrize("hq,hkv,d,dv,rotary", [(4, 2, 16, 16, 8), (6, 2, 16, 8, 16), (1, 1, 32, 40, 0), (3, 3, 10, 6, 4), (8, 1, 64, 64, 32)])
+def test_attention_with_head_norms_rotation_and_append(hq, hkv, d, dv, rotary, dtype, tol):
+    """Every head's query and key normed with one shared weight, then turned; keys and values land in shuffled
+    pages; the row-wise kernel (and, where it applies, the tensor-core kernel) over them gives the plain heads."""
+    from kapel_b200 import kernels as K
+
+    rng = np.random.default_rng(hq * 100 + d)
+    T = 70
+    nq, nk, nv = hq * d, hkv * d, hkv * dv
+    x = rng.standard_normal((T, nq + nk + nv))
+    wq, wk = rng.standard_normal(d), rng.standard_normal(d)
+    if dtype == torch.bfloat16:
+        wq, wk = bf16_round(wq), bf16_round(wk)
+    rot = {"base": 50.0, "dims": rotary} if rotary else None
+    pos = np.arange(T)
+    q = PK.rms_unit(x[:, :nq].reshape(T, hq, d), 1e-5) * wq
+    k = PK.rms_unit(x[:, nq : nq + nk].reshape(T, hkv, d), 1e-5) * wk
+    v = x[:, nq + nk :].reshape(T, hkv, dv)
+    if rot:
+        q, k = PK.rotate(q, pos, rot), PK.rotate(k, pos, rot)
+    want = np.zeros((T, hq, dv))
+    for a in range(hq):
+        want[:, a] = PK.causal_softmax((q[:, a] @ k[:, a // (hq // hkv)].T) * 0.3) @ v[:, a // (hq // hkv)]
+    n_pages, pages, lines = paged(rng, T)
+    kt = torch.zeros((n_pages, hkv, 16, d), dtype=dtype, device="cuda")
+    vt = torch.zeros((n_pages, hkv, 16, dv), dtype=dtype, device="cuda")
+    cs = K.rope_table(dev(pos, torch.int32), rotary, 50.0) if rotary else None
+    # in two portions, the second with a padding row in the middle that writes nowhere
+    cut = 33
+    lines2 = np.concatenate([lines[cut:50], [-1], lines[50:]])
+    x2 = np.concatenate([x[cut:50], x[49:50], x[50:]])
+    norms = ((dev(wq, dtype), 1e-5, 0.0), (dev(wk, dtype), 1e-5, 0.0))
+    q1 = K.head_norm_rope_append(dev(x[:cut]), 0, nq, nq + nk, norms[0], norms[1], cs[:cut].contiguous() if rotary else None, rotary,
+                                 dev(lines[:cut], torch.int32), kt, vt, hq, hkv, d, dv, True, dtype)
+    cs2 = torch.cat([cs[cut:50], cs[49:50], cs[50:]]).contiguous() if rotary else None
+    q2 = K.head_norm_rope_append(dev(x2), 0, nq, nq + nk, norms[0], norms[1], cs2, rotary, dev(lines2, torch.int32), kt, vt,
+                                 hq, hkv, d, dv, True, dtype)
+    keep = [i for i in range(len(x2)) if i != 50 - cut]
+    got_q = torch.cat([q1, q2[keep]]).float().cpu().numpy()
+    assert rel_err(got_q, q) < tol
+    table = dev(np.concatenate([pages, np.full(2, -1)])[None, :], torch.int32)
+    qd = torch.cat([q1, q2[keep]]).contiguous()
+    count = dev(pos + 1, torch.int32)
+    entry = torch.zeros(T, dtype=torch.int32, device="cuda")
+    got = K.paged_attention_rows(qd, kt, vt, table, entry, count, 16, None, 0.3, None, 1).float().cpu().numpy()
+    assert rel_err(got, want) < tol * 2
+    if dtype == torch.bfloat16 and dv == d and d % 16 == 0:
+        from kapel_b200.engine.batch import cut_tiles
+
+        per_tile = max(1, K.attention_mma_rows(False) // (hq // hkv))                     # tokens a tile of the kernel holds
+        tiles = tuple(dev(a, torch.int32) for a in cut_tiles(np.array([0]), np.array([T]), per_tile))
+        got = K.paged_attention_mma(qd, kt, vt, table, count, tiles, 16, None, 0.3, None, 0, 0, 1).float().cpu().numpy()
+        assert rel_err(got, want) < tol * 2
+
+
+def latent_reference(x_q, c, k_rot, uk, uv, sinks, H, d, r, e, scale):
+    """Plain heads from queries [T, H, d + r] (rotated part turned already), latents c [T, kv], rotated key parts [T, r]."""
+    T = x_q.shape[0]
+    k_plain = (c @ uk.T).reshape(T, H, d)
+    v = (c @ uv.T).reshape(T, H, e)
+    out = np.zeros((T, H, e))
+    for a in range(H):
+        s = (x_q[:, a, :d] @ k_plain[:, a].T + x_q[:, a, d:] @ k_rot.T) * scale
+        out[:, a] = PK.causal_softmax(s, None if sinks is None else float(sinks[a])) @ v[:, a]
+    return out
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 3e-2)])
+@pytest.mark.parametrize("H,d,r,e,q_rank,kv,T", [(3, 8, 4, 16, 24, 12, 300), (1, 16, 16, 8, 8, 40, 40), (10, 12, 6, 5, 20, 33, 70), (4, 32, 32, 32, 64, 64, 530)])
+def test_attention_through_latents_with_a_sink(H, d, r, e, q_rank, kv, T, dtype, tol):
+    """The latents' norms, the one rotated key part, the append; queries carried into the latent's space; all heads on
+    the one cached line whose first part is the value; the sink in the denominator; values back out through uv with
+    the gate. Keys cross pages and the row-wise kernel's chunks; more than eight heads run as two slices."""
+    from kapel_b200 import kernels as K
+
+    rng = np.random.default_rng(H * 10 + d)
+    rd = (lambda a: bf16_round(a)) if dtype == torch.bfloat16 else (lambda a: a)
+    stacked = rng.standard_normal((T, q_rank + kv + r + H * e))
+    wq, wkv = rd(rng.standard_normal(q_rank)), rd(rng.standard_normal(kv))
+    uq = rd(rng.standard_normal((H * (d + r), q_rank)) / q_rank ** 0.5)
+    uk = rd(rng.standard_normal((H * d, kv)) / kv ** 0.5)
+    uv = rd(rng.standard_normal((H * e, kv)) / kv ** 0.5)
+    sinks = rng.standard_normal(H) * 2
+    pos = np.arange(T)
+    rot = {"base": 40.0, "dims": r}
+    n_pages, pages, lines = paged(rng, T)
+    table = torch.zeros((n_pages, 1, 16, kv + r), dtype=dtype, device="cuda")
+    cs = K.rope_table(dev(pos, torch.int32), r, 40.0)
+    c_q = K.latent_append(dev(stacked), 0, q_rank, q_rank, kv, r, dev(wq, dtype), dev(wkv, dtype), 1e-5, cs, dev(lines, torch.int32),
+                          table, True, dtype)
+    want_cq = PK.rms_unit(stacked[:, :q_rank], 1e-5) * wq
+    assert rel_err(c_q.float().cpu().numpy(), want_cq) < tol
+    want_c = PK.rms_unit(stacked[:, q_rank : q_rank + kv], 1e-5) * wkv
+    want_kr = PK.rotate(stacked[:, None, q_rank + kv : q_rank + kv + r], pos, rot)[:, 0]
+    flat = table.float().cpu().numpy().reshape(-1, kv + r)[lines]
+    assert rel_err(flat[:, :kv], want_c) < tol and rel_err(flat[:, kv:], want_kr) < tol
+    # queries from the plain latent (so that the comparison below is about the attention alone)
+    q = (rd(want_cq) @ uq.T).reshape(T, H, d + r)
+    q_turned = np.concatenate([q[..., :d], PK.rotate(q[..., d:], pos, rot)], axis=-1)
+    m_uk = dev(uk.reshape(H, d, kv), dtype)
+    q_lat = K.head_linear(dev(q.reshape(T, -1)), H, d + r, 0, m_uk, y_head=kv + r, tail_off=d, tail=r, cos_sin=cs)
+    count, entry = dev(pos + 1, torch.int32), torch.zeros(T, dtype=torch.int32, device="cuda")
+    bt = dev(np.concatenate([pages, [-1]])[None, :], torch.int32)
+    slots = -(-T // K.attention_chunk())
+    y = K.paged_attention_rows(q_lat.view(T, H, kv + r), table, table, bt, entry, count, 16, None, 0.27, None, slots,
+                               sinks=dev(sinks), value_dim=kv)
+    m_uv = dev(uv.reshape(H, e, kv).transpose(0, 2, 1), dtype)
+    o = K.head_linear(y.view(T, H * kv), H, kv, 0, m_uv, gate=dev(stacked), g_off=q_rank + kv + r, pad_to=H * e + 3)
+    assert float(o[:, H * e :].abs().max()) == 0.0
+    want = latent_reference(q_turned, rd(want_c) if dtype == torch.bfloat16 else want_c, rd(want_kr) if dtype == torch.bfloat16 else want_kr,
+                            uk, uv, sinks, H, d, r, e, 0.27)
+    want = want * PK.sigmoid(stacked[:, q_rank + kv + r :]).reshape(T, H, e)
+    assert rel_err(o[:, : H * e].float().cpu().numpy().reshape(T, H, e), want) < tol
+
+
+def test_a_sink_takes_its_share_and_a_far_key_is_found():
+    """Scores made so that faults show: one key (far back, at page and chunk borders, the first, the row's own)
+    stands out by 25, so a row that sees it returns its value, and half of it against a sink of 25; a row just
+    before it does not see it; a huge sink silences the head. For rows of a prompt and for single tokens."""
+    from kapel_b200 import kernels as K
+
+    rng = np.random.default_rng(5)
+    H, d, dv, T = 2, 16, 12, 600
+    n_pages, pages, lines = paged(rng, T)
+    base = rng.standard_normal((T, d)) * 0.3
+    base[:, d - 1] = 0.0                                                                  # the marker's place, outside the value part
+    kt = torch.zeros((n_pages, 1, 16, d), dtype=torch.float32, device="cuda")
+    flat = kt.view(-1, d)
+    where = dev(lines, torch.int64)
+    bt = dev(np.concatenate([pages, [-1]])[None, :], torch.int32)
+    chunk = K.attention_chunk()
+    for target in (0, 1, 15, 16, 17, chunk - 1, chunk, chunk + 1, 2 * chunk, T - 2):
+        stored = base.copy()
+        stored[target, d - 1] = 1.0
+        flat[where] = dev(stored)
+        for rows in ([T - 1], [max(target - 1, 0), target, target + 1, T - 1]):           # a single token; rows of a prompt
+            q = rng.standard_normal((len(rows), H, d)) * 0.2
+            q[..., d - 1] = 25.0
+            for sinks in (np.array([-30.0, 25.0]), np.array([60.0, 3.0])):
+                y = K.paged_attention_rows(dev(q), kt, kt, bt, torch.zeros(len(rows), dtype=torch.int32, device="cuda"),
+                                           dev(np.array(rows) + 1, torch.int32), 16, None, 1.0, None, -(-T // chunk), sinks=dev(sinks),
+                                           value_dim=dv).cpu().numpy()
+                for i, r in enumerate(rows):
+                    for a in range(H):
+                        sc = stored[: r + 1] @ q[i, a]
+                        top = max(sc.max(), sinks[a])
+                        p = np.exp(sc - top)
+                        want = (p / (p.sum() + np.exp(sinks[a] - top))) @ stored[: r + 1, :dv]
+                        assert np.abs(y[i, a] - want).max() < 2e-5, (target, r, a)
+                    if sinks[0] > 40:
+                        assert np.abs(y[i, 0]).max() < 1e-6                               # the sink outweighs every key
+                    elif r >= target:
+                        assert np.abs(y[i, 0] - stored[target, :dv]).max() < 1e-3         # the far key is found ...
+                        assert np.abs(y[i, 1] - 0.5 * stored[target, :dv]).max() < 0.2    # ... and shares with the sink
+                    elif r > 0:
+                        assert np.abs(y[i, 0] - stored[target, :dv]).max() > 1e-2         # a row before the key does not see it
+
+
+@pytest.mark.parametrize("H,G,d,e,taps", [(4, 2, 16, 24, 3), (1, 1, 24, 20, 1), (2, 2, 40, 8, 4), (3, 1, 130, 5, 8)])
+def test_delta_rule_in_portions_and_token_by_token_against_plain(H, G, d, e, taps):
+    """Three requests of unequal length: whole, then in portions down to two tokens beside each other's single tokens,
+    through slots that are used again; the memory and the convolutions' history carry across steps."""
+    from kapel_b200 import kernels as K
+
+    rng = np.random.default_rng(d)
+    lengths = {"a": 150, "b": 37, "c": 64}
+    n, nv = G * d, H * e
+    width = 2 * n + nv + 2 * H
+    conv = rng.standard_normal((2 * n + nv, taps)) * 0.6
+    a_log, dt_bias = rng.standard_normal(H) * 0.5, rng.standard_normal(H)
+    data, want = {}, {}
+    for name, T in lengths.items():
+        x = rng.standard_normal((T, width))
+        x[:, -2 * H :] *= 3.0                               # decays and step sizes that swing
+        data[name] = x
+        q, k, v, g, beta = PK.delta_inputs(x, conv, a_log, dt_bias, H, G, d, e)
+        want[name] = np.stack([PK.delta_recurrence(q[:, h // (H // G)], k[:, h // (H // G)], v[:, h], g[:, h], beta[:, h]) for h in range(H)], axis=1)
+    per = K.delta_state_floats(H, G, d, e, taps)
+    state = torch.zeros((3, per), dtype=torch.float32, device="cuda")
+    cv, al, db = dev(conv), dev(a_log), dev(dt_bias)
+
+    def run(step):                                           # step: [(name, slot, a, b)]
+        rows = np.concatenate([data[n_][a:b] for n_, _, a, b in step])
+        entry = dev(np.concatenate([np.full(b - a, i) for i, (_, _, a, b) in enumerate(step)]), torch.int32)
+        ranges = K.entry_ranges(entry, len(step))
+        rows = dev(rows)
+        if len(rows) <= 4:                                   # a few rows come as split-K partial sums, as a small product leaves them
+            upper = (rows.view(torch.int32) & -4096).view(torch.float32)
+            rows = K.SplitSum(torch.stack([upper, rows - upper, torch.zeros_like(rows)]).contiguous())
+        out = K.delta_scan(rows, 0, n, 2 * n, 2 * n + nv, 2 * n + nv + H, cv, al, db, state, entry, ranges,
+                           dev([s for _, s, _, _ in step], torch.int32), len(step), H, G, d, e, taps, d ** -0.5, 1e-6).cpu().numpy()
+        at = 0
+        for n_, _, a, b in step:
+            err = float(np.abs(out[at : at + b - a] - want[n_][a:b]).max() / np.abs(want[n_]).max())
+            assert err < 5e-5, f"{n_}[{a}:{b}]: {err:.2e}"
+            at += b - a
+
+    run([("a", 1, 0, 150), ("b", 2, 0, 37)])                 # whole
+    state.zero_()
+    run([("a", 1, 0, 2), ("b", 2, 0, 30)])                   # portions, a's first of two tokens (shorter than the history)
+    run([("b", 2, 30, 31), ("a", 1, 2, 99)])
+    for i in range(6):                                       # b token by token beside a's portions of two
+        run([("a", 1, 99 + 2 * i, 101 + 2 * i), ("b", 2, 31 + i, 32 + i)])
+    state[2].zero_()                                         # b is finished; c takes its slot
+    run([("c", 2, 0, 3), ("a", 1, 111, 150)])
+    for i in range(3, 64):
+        run([("c", 2, i, i + 1)])
+    # rows of no request (slot 0) give zeros and leave every state alone
+    before = state.clone()
+    entry = dev([0, 1, 2, 3], torch.int32)
+    out = K.delta_scan(dev(data["a"][:4]), 0, n, 2 * n, 2 * n + nv, 2 * n + nv + H, cv, al, db, state, entry, K.entry_ranges(entry, 4),
+                       dev([0, 0, 0, 0], torch.int32), 4, H, G, d, e, taps, d ** -0.5, 1e-6)
+    assert float(out.abs().max()) == 0.0 and torch.equal(before, state)
+
+
+def test_delta_rule_recalls_what_it_stored_and_forgets_by_its_decay():
+    """A hand case: with step size one and no decay, orthogonal unit keys store their values exactly, and a later
+    write under the same key replaces the value; with a decay the first value fades by the product of the decays."""
+    d, e = 4, 3
+    k = np.eye(d)[[0, 1, 0, 2]].astype(np.float64)
+    v = np.arange(12, dtype=np.float64).reshape(4, e) + 1
+    q = np.eye(d)[[0, 0, 0, 0]].astype(np.float64)
+    out = PK.delta_recurrence(q, k, v, np.ones(4), np.ones(4))
+    assert np.allclose(out[0], v[0]) and np.allclose(out[1], v[0]) and np.allclose(out[2], v[2]) and np.allclose(out[3], v[2])
+    out = PK.delta_recurrence(q, k, v, np.array([1.0, 0.5, 1.0, 0.5])[:], np.array([1.0, 1.0, 0.0, 1.0]))
+    assert np.allclose(out[1], 0.5 * v[0]) and np.allclose(out[2], 0.5 * v[0]) and np.allclose(out[3], 0.25 * v[0])
+
+
+def test_gate_kernel_with_a_silu_gate_and_a_weight_shared_by_heads():
+    from kapel_b200 import kernels as K
+
+    rng = np.random.default_rng(2)
+    rows, heads, e = 9, 3, 20
+    y, z, w = rng.standard_normal((rows, heads, e)), rng.standard_normal((rows, 5 + heads * e)), rng.standard_normal(e)
+    got = K.head_gate(dev(y), dev(z), 5, dev(np.tile(w, heads)), True, 1e-5, torch.float32, gate_act="silu").cpu().numpy()
+    want = PK.rms_unit(y, 1e-5) * w * PK.silu(z[:, 5:]).reshape(rows, heads, e)
+    assert rel_err(got, want.reshape(rows, -1)) < 1e-5
+
+
+# -------------------------------------------------------------------------------------- the engine
+def engine_for(models, name, dtype, **kw):
+    from kapel_b200.engine import Engine
+
+    kw.setdefault("max_tokens", 1024)
+    kw.setdefault("max_sequences", 4)
+    return Engine.from_dir(models[name][0], dtype=dtype, **kw)
+
+
+def test_the_loop_gives_every_pass_a_cache_of_its_own(models):
+    eng = engine_for(models, "A", "float32")
+    assert len(eng.spec.schedule) == 1 + 2 * 3 + 1 and sum(e.before is not None for e in eng.spec.schedule) == 3
+    assert len(eng.cache.states) == 2 and sum(len(g.layers) for g in eng.cache.groups) == 6
+    latent = [g for g in eng.cache.groups if g.needs.shared_values][0]
+    k, v = eng.cache.tables(latent.layers[0])
+    assert k is v and k.shape[1] == 1 and k.shape[3] == 12 + 4                           # one line holds the latent and the rotated part
+    no_loop = engine_for(models, "B", "float32")
+    assert [e.replica for e in no_loop.spec.schedule] == [0, 0, 0] and not no_loop.model.merges
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_prompts_portions_and_decoding_against_plain(models, name, dtype):
+    """A prompt whole; the same prompt in portions of changing size down to two tokens and then
+    token by token (a long decoding that crosses pages); logits at every position."""
+    raw = models[name][1]
+    rng = np.random.default_rng(7)
+    tokens = random_tokens(rng, 150, raw["vocab"])
+    want = {"w": plain(models, name, tokens), "p": plain(models, name, tokens)}
+    eng = engine_for(models, name, dtype)
+    tb = TraceBuilder()
+    tb.step([("w", tokens, range(len(tokens)))], end=["w"])
+    at = 0
+    for n in (2, 17, 3, 2, 40, 5):
+        tb.step([("p", tokens[at : at + n], range(n))])
+        at += n
+    while at < len(tokens):
+        tb.step([("p", tokens[at : at + 1], [0])], end=(["p"] if at + 1 == len(tokens) else []))
+        at += 1
+    worst = check_rows(run_trace_engine(eng, tb.steps), tb, want, dtype, f"{name} {dtype}")
+    print(f"kofutar {name} {dtype}: worst {worst:.2e}")
+    assert eng.cache.free_pages() == eng.cache.total_pages() and eng.cache.free_slots() == 4
+
+
+def test_the_residual_after_every_layer_run_against_plain(models):
+    """In 32-bit, the stream after every layer run (a looped layer counts each time) is the plain one."""
+    from kapel_b200.engine import StepEntry
+
+    folder, raw, t = models["A"]
+    tokens = random_tokens(np.random.default_rng(1), 21, raw["vocab"])
+    plain_runs = []
+    PK.forward(raw, t, tokens, plain_runs)
+    eng = engine_for(models, "A", "float32")
+    seen = []
+    eng.model.tap = lambda i, x: seen.append(x.detach().cpu().numpy().copy())
+    eng.step([StepEntry("r", tokens, [])])
+    assert len(seen) == len(plain_runs) == 8
+    for i, (got, want) in enumerate(zip(seen, plain_runs)):
+        assert rel_err(got, want) < 2e-5, f"layer run {i}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_mixed_batches_and_reused_slots_against_each_alone(models, name, dtype):
+    """Up to four unequal requests a step, portions beside single tokens, a request left out of a
+    step, requests that end and whose pages and slots the next ones take; a pool of few pages."""
+    raw = models[name][1]
+    rng = np.random.default_rng(8)
+    reqs = {k: random_tokens(rng, n, raw["vocab"]) for k, n in dict(a=90, b=41, c=23, d=70, e=33, f=18).items()}
+    want = {k: plain(models, name, v) for k, v in reqs.items()}
+    eng = engine_for(models, name, dtype, max_tokens=64 * 2 + 128 * 2)
+    tb = TraceBuilder()
+    fed = {k: 0 for k in reqs}
+
+    def take(k, n, want_all=True):
+        a = fed[k]
+        n = min(n, len(reqs[k]) - a)
+        fed[k] += n
+        return (k, reqs[k][a : a + n], list(range(n)) if want_all else [n - 1])
+
+    done = lambda k: fed[k] == len(reqs[k])
+    tb.step([take("a", 30), take("b", 2), take("c", 23)], end=["c"])
+    tb.step([take("a", 1), take("b", 20), take("d", 17)])
+    tb.step([take("b", 1), take("d", 2), take("e", 33, False)], end=["e"])            # a is left out of this step
+    tb.step([take("a", 40), take("b", 1), take("d", 1), take("f", 5)])
+    while not all(done(k) for k in "abdf"):
+        entries = [take(k, 1) for k in "abdf" if not done(k)]
+        tb.step(entries, end=[k for k, _, _ in entries if done(k)])
+    worst = check_rows(run_trace_engine(eng, tb.steps), tb, want, dtype, f"{name} {dtype}")
+    print(f"kofutar mixed {name} {dtype}: worst {worst:.2e}")
+    eng.cache.check()
+    assert eng.cache.free_pages() == eng.cache.total_pages() and eng.cache.free_slots() == 4
+
+
+def test_recorded_passes_leave_the_state_as_eager_ones_do(models):
+    """A prompt pass of a shape seen before and a decoding pass go through recordings, whose first
+    eager run must not advance the memory or the convolutions' history a second time."""
+    raw = models["A"][1]
+    outs = []
+    for graphs in (False, True):
+        eng = engine_for(models, "A", "float32", graphs=graphs)
+        tb = TraceBuilder()
+        for k in ("x", "y", "z"):                            # the same shape three times: eager, recorded, replayed
+            tokens = random_tokens(np.random.default_rng(ord(k)), 80, raw["vocab"])
+            tb.step([(k, tokens[:70], [69])])
+            for i in range(70, 80):
+                tb.step([(k, tokens[i : i + 1], [0])], end=([k] if i == 79 else []))
+        outs.append(run_trace_engine(eng, tb.steps))
+        if graphs:
+            assert eng.recorded_passes > 0
+    for step in outs[0]:
+        assert rel_err(outs[1][step], outs[0][step]) < 2e-6, f"step {step}"
+
+
+ODD = {"architecture": "Kofutar", "vocab": 77, "width": 52, "norm": {"eps": 1e-6}, "loop": {"start": 1, "stop": 2, "times": 2}, "layers": [
+    attention_layer(3, 1, 12, 10, 0.3, {"base": 80.0, "dims": 6}, 13),
+    latent_layer(3, 10, 6, 7, 11, 9, 0.3, 60.0, None),
+    delta_layer(3, 3, 10, 6, 2, 11)]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_are_no_multiples_of_eight(dtype, tmp_path):
+    """A width, head sizes, ranks and feed-forward sizes that fit no 16-byte piece: the bfloat16 products run
+    on zero-padded rows, the other kernels value by value."""
+    from kapel_b200.engine import Engine
+
+    folder = make_folder(ODD, 6, tmp_path)
+    t = read_tensors(folder)
+    eng = Engine.from_dir(folder, dtype=dtype, max_tokens=512, max_sequences=4)
+    tokens = random_tokens(np.random.default_rng(3), 95, ODD["vocab"])
+    want = {"a": PK.forward(ODD, t, tokens)}
+    tb = TraceBuilder()
+    tb.step([("a", tokens[:70], range(70))])
+    tb.step([("a", tokens[70:73], range(3))])
+    for i in range(73, 95):
+        tb.step([("a", tokens[i : i + 1], [0])], end=(["a"] if i == 94 else []))
+    check_rows(run_trace_engine(eng, tb.steps), tb, want, dtype, f"odd {dtype}")
+
+
+def test_a_prompt_longer_than_the_attention_kernels_chunks(models):
+    """700 tokens: the row-wise kernel's chunks of keys are merged, the sink counted once; a portion that starts
+    in the middle of a chunk; then single tokens."""
+    raw = models["C"][1]
+    tokens = random_tokens(np.random.default_rng(12), 700, raw["vocab"])
+    want = {"a": plain(models, "C", tokens)}
+    eng = engine_for(models, "C", "float32")
+    tb = TraceBuilder()
+    tb.step([("a", tokens[:300], [0, 255, 256, 299])])
+    tb.step([("a", tokens[300:690], [0, 211, 212, 389])])
+    for i in range(690, 700):
+        tb.step([("a", tokens[i : i + 1], [0])], end=(["a"] if i == 699 else []))
+    check_rows(run_trace_engine(eng, tb.steps), tb, want, "float32", "long")
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point_and_scheduler(models, name):
+    """`Model.generate` and `generate_batch` (prompt portions under a token budget, decoding passes
+    staged and recorded) give the plain implementation's greedy tokens."""
+    import kapel_b200
+
+    folder, raw, t = models[name]
+    rng = np.random.default_rng(10)
+    prompts = [random_tokens(rng, n, raw["vocab"]) for n in (3, 29, 75)]
+
+    def plain_greedy(prompt, n):
+        seq, margins = list(prompt), []
+        for _ in range(n):
+            row = PK.forward(raw, t, seq)[-1]
+            order = np.argsort(row)
+            margins.append(float(row[order[-1]] - row[order[-2]]))
+            seq.append(int(order[-1]))
+        return seq[len(prompt):], margins
+
+    want = [plain_greedy(p, 12) for p in prompts]
+    model = kapel_b200.Model(str(folder), dtype="f32", max_tokens_cached=1024, max_sequences=4, max_pass_tokens=32)
+    for p, (tokens, margins) in zip(prompts, want):
+        safe = next((i for i, m in enumerate(margins) if m < 1e-3), len(margins))
+        assert model.generate(p, max_tokens=12)[:safe] == tokens[:safe]
+    together = model.generate_batch(prompts, max_tokens=12)
+    for got, (tokens, margins) in zip(together, want):
+        safe = next((i for i, m in enumerate(margins) if m < 1e-3), len(margins))
+        assert got[:safe] == tokens[:safe]
+    assert model.engine.cache.free_pages() == model.engine.cache.total_pages()
+
+
+def test_replay_program_and_command_line(models, tmp_path):
+    """`bin/trace_run` and `python -m kapel_b200 run` take a Kofutar folder as they take any other: the
+    program's logits are the plain ones, the command's greedy tokens are the entry point's."""
+    import subprocess
+    import sys
+
+    import kapel_b200
+    from helpers import ROOT
+
+    folder, raw, _ = models["A"]
+    tokens = random_tokens(np.random.default_rng(4), 40, raw["vocab"])
+    want = plain(models, "A", tokens)
+    steps = [{"step": 0, "entries": [{"id": "q", "tokens": tokens[:33], "want": [0, 32]}], "end": []},
+             {"step": 1, "entries": [{"id": "q", "tokens": tokens[33:35], "want": []}], "end": []},
+             {"step": 5, "entries": [{"id": "q", "tokens": tokens[35:], "want": [4]}], "end": ["q"]}]
+    out = tmp_path / "logits"
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "64"], input="".join(json.dumps(x) + "\n" for x in steps), capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr
+    assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == ["done 0", "done 1", "done 5"]
+    assert sorted(f.name for f in out.iterdir()) == ["0.f32", "5.f32"]
+    first = np.fromfile(out / "0.f32", dtype="<f4").reshape(2, raw["vocab"])
+    last = np.fromfile(out / "5.f32", dtype="<f4").reshape(1, raw["vocab"])
+    assert rel_err(first, want[[0, 32]]) < TOL["float32"] and rel_err(last, want[[39]]) < TOL["float32"]
+
+    model = kapel_b200.Model(str(folder), dtype="f32", max_tokens_cached=256, max_sequences=2)
+    expect = model.generate(tokens[:9], max_tokens=6)
+    r = subprocess.run([sys.executable, "-m", "kapel_b200", "run", str(folder), "--tokens", ",".join(map(str, tokens[:9])), "--max-tokens", "6",
+                        "--greedy", "--dtype", "f32"], capture_output=True, text=True, timeout=900, cwd=str(ROOT))
+    assert r.returncode == 0, r.stderr
+    assert [int(x) for x in r.stdout.strip().splitlines()[0].split(",")] == expect
