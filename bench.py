@@ -1,7 +1,7 @@
 """Throughput of the engine at Gemma 2 sizes with random weights, on one GPU.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--size 2b|9b|27b] [--layers L] [--impl reference]
-    python bench.py --design fusitar [--design-sizes s,m]      (another line: see `design_line`)
+    python bench.py --design fusitar|kofutar [--design-sizes s,m]      (another line: see `design_line`)
 
 A "step" is one decode step. The default run has the layer sizes of the 2B configuration
 (26 layers, hidden 2304, 8 heads over 4 kv heads of 256, intermediate 9216, vocabulary 256000,
@@ -386,6 +386,27 @@ def fusitar_config(z):
             "norm": {"eps": 1e-6}, "layers": [att if i % 2 == 0 else rec for i in range(z["layers"])]}
 
 
+# --design kofutar: the Kofutar design (attention with per-head norms, attention through latents with a sink,
+# the gated delta rule, a dense gated feed-forward, layer norms) beside Fusitar, the engine's other design with
+# recurrent and attending layers, and Gemma 2, whose dense feed-forward it shares, at equal sizes: the same width,
+# heads, head size, vocabulary, as many layers, Gemma's intermediate size. Its layers take turns: attention, delta,
+# latent attention, delta; the loop covers them all once (so the input mix runs). The latents have the sizes usual
+# for such layers: three quarters of the width for the queries, 512 + 64 rotated for keys and values.
+def kofutar_config(z):
+    mlp = {"kind": "dense", "ff": z["top"] * z["ff"]}
+    att = {"type": "attention", "mlp": mlp, "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                                                        "scale": z["dim"] ** -0.5, "rot": {"base": 10000.0, "dims": z["dim"]}}}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": z["heads"], "dim": z["dim"], "rot_dim": 64, "vdim": z["dim"], "q_rank": z["width"] * 3 // 4, "kv_rank": KOFUTAR_KV_RANK,
+                     "scale": (z["dim"] + 64) ** -0.5, "rot": {"base": 10000.0, "dims": 64}}}
+    rec = {"type": "delta", "mlp": mlp, "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "conv": 4}}
+    return {"architecture": "Kofutar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "loop": {"start": 0, "stop": z["layers"], "times": 1}, "layers": [(att, rec, lat, rec)[i % 4] for i in range(z["layers"])]}
+
+
+KOFUTAR_KV_RANK = 512
+
+
 def gemma_config(z):
     return {"architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2", "num_hidden_layers": z["layers"], "hidden_size": z["width"],
             "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"], "head_dim": z["dim"],
@@ -399,6 +420,17 @@ def design_kernel_rooflines(which, z, kind, rows, context, batch, pk):
     tokens of one request from position 0) or "decode" (batch requests of `context` positions)."""
     w, hq, hkv, d, win = z["width"], z["heads"], z["kv_heads"], z["dim"], z["window"]
     layers = z["layers"]
+    if which == "kofutar":
+        att_layers, lat_layers, rec_layers = (layers + 3) // 4, (layers + 1) // 4, layers // 2
+        r, kv, ff = 64, KOFUTAR_KV_RANK, z["top"] * z["ff"]
+        if kind == "prefill":
+            pairs = rows * (rows + 1) // 2
+            # the latent layers by what the design asks for (a head's own keys of d + r and values of d), not by the
+            # longer lines the kernel walks; the delta rule: decay, two read-outs and the update of a [d, d] memory a row and head
+            return {"attention": ("flops", att_layers * 4.0 * pairs * hq * d), "latent_attention": ("flops", lat_layers * 2.0 * pairs * hq * (2 * d + r)),
+                    "feed_forward": ("flops", layers * 2.0 * rows * 3 * ff * w), "delta_scan": ("flops", rec_layers * 7.0 * rows * hq * d * d)}
+        return {"attention": ("bytes", att_layers * batch * context * hkv * d * 2 * 2.0), "latent_attention": ("bytes", lat_layers * batch * context * (kv + r) * 2.0),
+                "feed_forward": ("bytes", layers * 3.0 * ff * w * 2), "delta_scan": ("bytes", rec_layers * batch * hq * d * d * 4 * 2.0)}
     att_layers = layers if which == "gemma2" else (layers + 1) // 2
     rec_layers = 0 if which == "gemma2" else layers // 2
     out = {}
@@ -421,6 +453,13 @@ KERNEL_CLASSES = {
     "feed_forward": ("moe_grouped", "gemm_glu_fused", "glu", "gemm:ffn"),
     "mlstm_scan": ("mlstm_scan",),
 }
+# Kofutar's attention layers run the tensor-core kernels; the row-wise kernel is its latent layers', with the products a head around it.
+KOFUTAR_KERNEL_CLASSES = {
+    "attention": ("paged_attention_mma", "paged_attention_decode_fused"),
+    "latent_attention": ("paged_attention_rows", "head_linear"),
+    "feed_forward": ("gemm_glu_fused", "glu"),
+    "delta_scan": ("delta_scan",),
+}
 
 
 def design_point(which, z, steps, warmup, clocks, pk):
@@ -432,7 +471,7 @@ def design_point(which, z, steps, warmup, clocks, pk):
     from kapel_b200 import kernels as K
     from kapel_b200.engine import Engine, StepEntry
 
-    cfg = fusitar_config(z) if which == "fusitar" else gemma_config(z)
+    cfg = {"fusitar": fusitar_config, "kofutar": kofutar_config, "gemma2": gemma_config}[which](z)
     room = (DESIGN_BATCH + 1) * (DESIGN_HISTORY + 4 * (steps + warmup) + 128) + PREFILL_TOKENS
     engine = Engine.random(cfg, seed=0, dtype="bfloat16", max_tokens=room, max_sequences=DESIGN_BATCH + 2)
     rng = np.random.default_rng(0)
@@ -477,12 +516,14 @@ def design_point(which, z, steps, warmup, clocks, pk):
         must = design_kernel_rooflines(which, z, kind, PREFILL_TOKENS, DESIGN_HISTORY, DESIGN_BATCH, pk)
         classes = {}
         for name, shape, calls, ms in rows:
-            for cls, members in KERNEL_CLASSES.items():
+            for cls, members in (KOFUTAR_KERNEL_CLASSES if which == "kofutar" else KERNEL_CLASSES).items():
                 if name in members:
                     classes[cls] = classes.get(cls, 0.0) + ms
-        if which == "gemma2":          # Gemma's way down is a plain product: count the products whose inner width is the intermediate size
+        if which in ("gemma2", "kofutar"):   # the dense way down is a plain product: count the products whose inner width is the intermediate size
+            # (Kofutar's input mix has the same shape where the intermediate size is twice the width: one call more than the layers', taken off by its share)
             classes["feed_forward"] = classes.get("feed_forward", 0.0) + sum(
-                ms for name, shape, calls, ms in rows if name == "gemm" and len(shape) == 2 and shape[0] == z["width"] and shape[1] == z["top"] * z["ff"])
+                ms * (z["layers"] / calls if (which == "kofutar" and calls == z["layers"] + 1) else 1.0)
+                for name, shape, calls, ms in rows if name == "gemm" and len(shape) == 2 and shape[0] == z["width"] and shape[1] == z["top"] * z["ff"])
         rec = {"kernels": [{"name": n, "shape": list(sh), "calls": c, "ms": round(ms, 4)} for n, sh, c, ms in rows][:14], "classes": {}}
         for cls, ms in classes.items():
             unit, amount = must[cls]
@@ -510,14 +551,16 @@ def design_line(args) -> int:
     sizes = {}
     for name in args.design_sizes.split(","):
         z = DESIGN_SIZES[name]
-        sizes[name] = {"shape": z, "fusitar": design_point("fusitar", z, min(args.steps, 50), max(3, args.warmup), clocks, pk),
-                       "gemma2": design_point("gemma2", z, min(args.steps, 50), max(3, args.warmup), clocks, pk)}
+        beside = ("gemma2",) if args.design == "fusitar" else ("fusitar", "gemma2")
+        sizes[name] = {"shape": z}
+        for which in (args.design,) + beside:
+            sizes[name][which] = design_point(which, z, min(args.steps, 50), max(3, args.warmup), clocks, pk)
     clocks.close()
     first = sizes[args.design_sizes.split(",")[0]]
     print(json.dumps({
-        "metric": f"decode tok/s at batch {DESIGN_BATCH} (Fusitar, size {args.design_sizes.split(',')[0]}, bf16, {DESIGN_HISTORY} tokens of history per sequence)",
-        "value": first["fusitar"]["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
-        "data": "synthetic: seeded random weights and uniform-random token ids", "design": "fusitar", "beside": "gemma2 at equal sizes",
+        "metric": f"decode tok/s at batch {DESIGN_BATCH} ({args.design.capitalize()}, size {args.design_sizes.split(',')[0]}, bf16, {DESIGN_HISTORY} tokens of history per sequence)",
+        "value": first[args.design]["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+        "data": "synthetic: seeded random weights and uniform-random token ids", "design": args.design, "beside": " and ".join(beside) + " at equal sizes",
         "config": {"peaks": pk["source"], "prefill_tokens": PREFILL_TOKENS}, "sizes": sizes, "clocks": clocks.summary(), "impl": "ours"}))
     return 0
 
@@ -538,8 +581,8 @@ def main() -> int:
     ap.add_argument("--skip-check", action="store_true", help="leave out the check of the timed logits against the 32-bit path")
     ap.add_argument("--breakdown", action="store_true",
                     help="instead of the JSON line: device time by kernel for one prefill step and one eager decode step")
-    ap.add_argument("--design", default=None, choices=["fusitar"],
-                    help="instead of the default line: this design beside Gemma 2 at equal sizes, prefill and decode, with each like kernel's roofline fraction")
+    ap.add_argument("--design", default=None, choices=["fusitar", "kofutar"],
+                    help="instead of the default line: this design beside Gemma 2 (kofutar: beside Fusitar and Gemma 2) at equal sizes, prefill and decode, with each like kernel's roofline fraction")
     ap.add_argument("--design-sizes", default="s,m", help="which of the design sizes (s, m), comma separated")
     args = ap.parse_args()
 
