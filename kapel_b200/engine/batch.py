@@ -241,6 +241,10 @@ class StepBatch:
         extra = -(-keep_first // self.chunk) if (window and keep_first) else 0
         return self._slots_memo[window] + extra
 
+    def longest_portion(self) -> int:
+        """The most rows any request brings in this step (what sizes a launch of a block a run of a request's rows)."""
+        return int(self.plan.q_len.max()) if len(self.plan.q_len) else 0
+
     def entry_ranges(self):
         """(start, end) on the device: rows [start[e], end[e]) are request e's. Made once a step."""
         if "entry_ranges" not in self.memo:

@@ -68,6 +68,9 @@ class StaticBatch:
         extra = -(-keep_first // self.chunk) if (window and keep_first) else 0
         return max(1, n) + extra
 
+    def longest_portion(self) -> int:
+        return 1                                             # every request brings one token
+
     def entry_ranges(self):
         """(start, end) on the device: rows [start[e], end[e]) are request e's (here every row is its own)."""
         if "entry_ranges" not in self.memo:

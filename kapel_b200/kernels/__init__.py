@@ -564,6 +564,43 @@ def paged_attention_rows(q, k_table, v_table, block_table, row_entry, row_count,
     return out
 
 
+def latent_attention_mma_takes(dtype, d: int, dv: int) -> bool:
+    """Whether the tensor-core kernel for attention over lines that are key and value at once takes
+    these sizes (else the row-wise kernel does)."""
+    return dtype == torch.bfloat16 and bool(library().kb_latent_attention_mma_takes(int(d), int(dv)))
+
+
+def latent_attention_mma(q, table, block_table, row_count, ranges, entries: int, longest: int, page_size: int, scale: float,
+                         slots: int, sinks: Optional[torch.Tensor], value_dim: int) -> torch.Tensor:
+    """Attention of every query head [rows, hq, d] over the lines of `table` [pages, 1, page_size, d],
+    whose first `value_dim` components are the values, on tensor cores (bfloat16). `ranges` =
+    (start, end) of each request's rows on the device, `longest` the most rows a request brings;
+    `slots` as for `paged_attention_rows` without a window. `sinks` [hq] float32 or None."""
+    rows, hq, d = q.shape
+    _need(q, "latent attention q", torch.bfloat16)
+    _need(table, "latent attention table", torch.bfloat16)
+    if table.dim() != 4 or table.shape[1] != 1 or table.shape[2] != page_size or table.shape[3] != d:
+        raise KernelError(f"latent attention: a table of {tuple(table.shape)} is not [pages, 1, {page_size}, {d}]")
+    _need(block_table, "latent attention block table", torch.int32)
+    _need(row_count, "latent attention row_count", torch.int32, (rows,))
+    start, end = ranges
+    _need(start, "latent attention entry starts", torch.int32)
+    _need(end, "latent attention entry ends", torch.int32)
+    if min(start.numel(), end.numel()) < entries or block_table.shape[0] < entries:
+        raise KernelError(f"latent attention: {entries} requests but ranges or block tables for fewer")
+    if sinks is not None:
+        _need(sinks, "latent attention sinks", torch.float32, (hq,))
+    dv = int(value_dim)
+    out = _fresh((rows, hq, dv), torch.bfloat16, q.device)
+    lib = library()
+    need = lib.kb_paged_attention_scratch_floats(rows, hq, dv, int(slots))
+    scratch = _fresh((need,), torch.float32, q.device) if need else None
+    _check(lib.kb_latent_attention_mma(_ptr(out), _ptr(q), _ptr(table), _ptr(block_table), _ptr(row_count), _ptr(start), _ptr(end),
+                                       int(entries), int(longest), rows, hq, d, dv, int(page_size), int(block_table.shape[1]),
+                                       int(table.shape[0]), int(slots), _f(scale), _ptr(scratch), _ptr(sinks), _stream()))
+    return out
+
+
 def attention_keep_slots(window: Optional[int], keep_first: int) -> int:
     """Chunk slots the row-wise kernel spends on the kept first keys of a windowed layer."""
     return -(-int(keep_first) // attention_chunk()) if (window and keep_first) else 0
@@ -1079,7 +1116,7 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, uni
 _TIMED = ("embed", "rope_table", "rope_append", "glu", "cast", "gather_rows", "rmsnorm", "add_rmsnorm", "gemm",
           "paged_attention_rows", "paged_attention_mma", "sample", "proj_norm_append", "head_gate", "mlstm_scan", "moe_route",
           "moe_sort", "moe_grouped", "moe_combine", "gemm_glu_fused", "paged_attention_decode_fused", "layernorm", "concat2",
-          "head_norm_rope_append", "latent_append", "head_linear", "delta_scan")
+          "head_norm_rope_append", "latent_append", "head_linear", "delta_scan", "latent_attention_mma")
 _timing = None
 _originals = {}
 

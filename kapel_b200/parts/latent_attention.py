@@ -12,7 +12,7 @@ output uv_h (sum_j p_j c_j) is one more small product a head, which also applies
     c_q, cache line                     `latent_append`: both RMS norms, the key part's rotation, the append
     q = uq c_q                          [rows, heads, head_dim + rot_dim]
     q' = [uk_h^T q_plain | rot(q_rot)]  `head_linear` with the rotation of the tail
-    y = attention(q', lines, sink)      row-wise kernel, the sink in the denominator
+    y = attention(q', lines, sink)      the tensor-core kernel for such lines (bfloat16) or the row-wise kernel; the sink in the denominator
     o = (uv_h y) * sigmoid(g)           `head_linear` with the gate, then the output product
 """
 from __future__ import annotations
@@ -84,9 +84,14 @@ class LatentAttention(Part):
                               cos_sin, group.lines, k_table, cache.owns, ctx.dtype, pad_to=self.w_uq.shape[1])
         q = linear(ctx, c_q, self.w_uq, out_dtype=torch.float32, keep_split=True)
         q_lat = K.head_linear(q, H, d + r, 0, self.m_uk, y_head=s.kv_rank + r, tail_off=d, tail=r, cos_sin=cos_sin)
-        y = K.paged_attention_rows(q_lat.view(-1, H, s.kv_rank + r), k_table, k_table, group.block_table, batch.row_entry,
-                                   batch.row_count, ctx.page_size, None, s.scale, None, batch.attention_slots(None),
-                                   sinks=self.sinks, value_dim=s.kv_rank)
+        if K.latent_attention_mma_takes(q_lat.dtype, s.kv_rank + r, s.kv_rank):
+            y = K.latent_attention_mma(q_lat.view(-1, H, s.kv_rank + r), k_table, group.block_table, batch.row_count, batch.entry_ranges(),
+                                       batch.entries, batch.longest_portion(), ctx.page_size, s.scale, batch.attention_slots(None),
+                                       self.sinks, s.kv_rank)
+        else:                   # the 32-bit path, and sizes the tensor-core kernel does not take
+            y = K.paged_attention_rows(q_lat.view(-1, H, s.kv_rank + r), k_table, k_table, group.block_table, batch.row_entry,
+                                       batch.row_count, ctx.page_size, None, s.scale, None, batch.attention_slots(None),
+                                       sinks=self.sinks, value_dim=s.kv_rank)
         o = K.head_linear(y.view(-1, H * s.kv_rank), H, s.kv_rank, 0, self.m_uv, gate=stacked if s.gated else None,
                           g_off=s.q_rank + s.kv_rank + r, pad_to=product_width(ctx, H * s.v_head_dim))
         return linear(ctx, o, self.w_o, keep_split=True)
