@@ -456,7 +456,7 @@ KERNEL_CLASSES = {
 # Kofutar's attention layers run the tensor-core kernels; the row-wise kernel is its latent layers', with the products a head around it.
 KOFUTAR_KERNEL_CLASSES = {
     "attention": ("paged_attention_mma", "paged_attention_decode_fused"),
-    "latent_attention": ("paged_attention_rows", "head_linear"),
+    "latent_attention": ("paged_attention_rows", "latent_attention_mma", "head_linear"),
     "feed_forward": ("gemm_glu_fused", "glu"),
     "delta_scan": ("delta_scan",),
 }

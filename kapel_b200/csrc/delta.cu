@@ -18,7 +18,8 @@
 // request of the step x one head x DC value components, a warp a component, lane l the memory's rows
 // j = l, l + 32, ... of that column in registers. Written with the decayed memory M = g S of a row:
 // a = M.k and b = M.q are reduced side by side (one round of shuffles a row), u = beta (v - a),
-// o = b + u (k.q), S = M + k u. The next row's inputs are loaded while this one is reduced. A
+// o = b + u (k.q), S = M + k u. The rows' inputs come into shared memory a chunk of rows at a time by
+// asynchronous copies, the next chunk while this one is walked. A
 // column of a head's memory lies together in the state table, so a warp reads and writes whole lines.
 #include "common.cuh"
 
@@ -144,74 +145,132 @@ __global__ void delta_history_kernel(const Src<TS> src, const DeltaParams p) {
         if (i < keep) hist[(size_t)i * channels + c] = fresh[i];
 }
 
-template <int R>
+__device__ __forceinline__ void delta_copy4(float* dst, const float* src) {
+    const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d32), "l"(src) : "memory");
+}
+__device__ __forceinline__ void delta_copy16(float* dst, const float* src) {
+    const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d32), "l"(src) : "memory");
+}
+
+// R: memory rows a lane holds (d <= 32 R); CH: rows of the step staged at a time. The rows' inputs (k, q, the block's
+// values, decay, step size, q.k) come into shared memory a chunk at a time by asynchronous copies, the next chunk
+// while this one is walked: a row's step then waits for shared memory only.
+template <int R, int CH>
 __global__ void __launch_bounds__(DC * 32)
 delta_scan_kernel(const DeltaParams p) {
+    extern __shared__ __align__(16) float staged[];             // [2][CH][rowf]
     const int entry = blockIdx.x, head = blockIdx.y;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int c = blockIdx.z * DC + warp;
     const int r0 = p.entry_start[entry], r1 = p.entry_end[entry];
-    if (r1 <= r0 || c >= p.e) return;
+    if (r1 <= r0) return;
     const int slot = p.slots[entry];
     const int d = p.d, e = p.e;
+    const bool live = c < e;
     if (slot <= 0 || slot >= p.n_slots) {                       // rows of no request: zeros, no state
-        if (lane == 0)
+        if (live && lane == 0)
             for (int r = r0; r < r1; ++r) p.out[((size_t)r * p.heads + head) * e + c] = 0.f;
         return;
     }
     const int nq = p.kv_heads * d, nv = p.heads * e;
     const int kvh = head / (p.heads / p.kv_heads);
-    float* st = p.state + (size_t)slot * p.state_floats + (size_t)(p.taps - 1) * (2 * nq + nv) + ((size_t)head * e + c) * d;
+    float* st = p.state + (size_t)slot * p.state_floats + (size_t)(p.taps - 1) * (2 * nq + nv) + ((size_t)head * e + (live ? c : 0)) * d;
     float S[R];
 #pragma unroll
-    for (int i = 0; i < R; ++i) S[i] = lane + 32 * i < d ? st[lane + 32 * i] : 0.f;
+    for (int i = 0; i < R; ++i) S[i] = (live && lane + 32 * i < d) ? st[lane + 32 * i] : 0.f;
 
-    float k[R], q[R], k2[R], q2[R];
-    float v, g, beta, kq, v2 = 0.f, g2 = 0.f, beta2 = 0.f, kq2 = 0.f;
-    auto fetch = [&](int r, float (&kk)[R], float (&qq)[R], float& vv, float& gg, float& bb, float& kkqq) {
-        const float* kp = p.kn + ((size_t)r * p.kv_heads + kvh) * d;
-        const float* qp = p.qn + ((size_t)r * p.kv_heads + kvh) * d;
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const int j = lane + 32 * i;
-            kk[i] = j < d ? kp[j] : 0.f;
-            qq[i] = j < d ? qp[j] : 0.f;
+    constexpr int DP = R * 32;                                  // k and q padded to the lanes' rows, zeros beyond d
+    constexpr int tail = 2 * DP;                                // v [DC] | decay | step size | q.k | padding
+    constexpr int rowf = 2 * DP + 8;
+    const bool wide = d % 4 == 0 && (((uintptr_t)p.kn | (uintptr_t)p.qn) & 15) == 0;
+    auto stage = [&](int chunk, int buf) {
+        const int rbase = r0 + chunk * CH;
+        const int nr = min(CH, r1 - rbase);
+        float* base = staged + (size_t)buf * CH * rowf;
+        for (int t = warp; t < nr; t += DC) {                   // a warp a row in turn
+            float* row = base + (size_t)t * rowf;
+            const float* kp = p.kn + ((size_t)(rbase + t) * p.kv_heads + kvh) * d;
+            const float* qp = p.qn + ((size_t)(rbase + t) * p.kv_heads + kvh) * d;
+            if (wide) {
+                for (int x = lane * 4; x < d; x += 128) {
+                    delta_copy16(row + x, kp + x);
+                    delta_copy16(row + DP + x, qp + x);
+                }
+            } else {
+                for (int x = lane; x < d; x += 32) {
+                    delta_copy4(row + x, kp + x);
+                    delta_copy4(row + DP + x, qp + x);
+                }
+            }
         }
-        vv = p.vn[((size_t)r * p.heads + head) * e + c];
-        gg = p.scal[((size_t)r * p.heads + head) * 2];
-        bb = p.scal[((size_t)r * p.heads + head) * 2 + 1];
-        kkqq = p.kq[(size_t)r * p.kv_heads + kvh];
+        for (int idx = tid; idx < nr * (DC + 3); idx += DC * 32) {
+            const int t = idx / (DC + 3), x = idx - t * (DC + 3);
+            float* dst = base + (size_t)t * rowf + tail + x;
+            const size_t r = (size_t)(rbase + t);
+            if (x < DC) {
+                const int cc = blockIdx.z * DC + x;
+                if (cc < e) delta_copy4(dst, p.vn + (r * p.heads + head) * e + cc);
+                else *dst = 0.f;
+            } else if (x < DC + 2) {
+                delta_copy4(dst, p.scal + (r * p.heads + head) * 2 + (x - DC));
+            } else {
+                delta_copy4(dst, p.kq + r * p.kv_heads + kvh);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    fetch(r0, k, q, v, g, beta, kq);
-    for (int r = r0; r < r1; ++r) {
-        if (r + 1 < r1) fetch(r + 1, k2, q2, v2, g2, beta2, kq2);
-        float a[2] = {0.f, 0.f}, b[2] = {0.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-            S[i] *= g;
-            a[i & 1] = fmaf(S[i], k[i], a[i & 1]);
-            b[i & 1] = fmaf(S[i], q[i], b[i & 1]);
+    if (d < DP) {                                               // the padding of k and q, once: no copy ever writes it
+        for (int idx = tid; idx < 2 * CH * 2 * (DP - d); idx += DC * 32) {
+            const int t = idx / (2 * (DP - d)), x = idx - t * 2 * (DP - d);
+            staged[(size_t)t * rowf + (x < DP - d ? d + x : DP + d + (x - (DP - d)))] = 0.f;
         }
-        float sa = a[0] + a[1], sb = b[0] + b[1];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            sa += __shfl_xor_sync(0xffffffffu, sa, o);
-            sb += __shfl_xor_sync(0xffffffffu, sb, o);
-        }
-        const float u = beta * (v - sa);
-#pragma unroll
-        for (int i = 0; i < R; ++i) S[i] = fmaf(k[i], u, S[i]);
-        if (lane == 0) p.out[((size_t)r * p.heads + head) * e + c] = fmaf(u, kq, sb);
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-            k[i] = k2[i];
-            q[i] = q2[i];
-        }
-        v = v2; g = g2; beta = beta2; kq = kq2;
     }
+    const int chunks = (r1 - r0 + CH - 1) / CH;
+    stage(0, 0);
+    for (int ch = 0; ch < chunks; ++ch) {
+        if (ch + 1 < chunks) {
+            stage(ch + 1, (ch + 1) & 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const int rbase = r0 + ch * CH;
+        const int nr = min(CH, r1 - rbase);
+        const float* rows = staged + (size_t)(ch & 1) * CH * rowf;
+        for (int t = 0; t < nr; ++t) {
+            const float* in = rows + (size_t)t * rowf;
+            const float v = in[tail + warp], g = in[tail + DC], beta = in[tail + DC + 1], kq = in[tail + DC + 2];
+            float k[R], q[R];
+            float a[2] = {0.f, 0.f}, b[2] = {0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < R; ++i)
-        if (lane + 32 * i < d) st[lane + 32 * i] = S[i];
+            for (int i = 0; i < R; ++i) {
+                k[i] = in[lane + 32 * i];
+                q[i] = in[DP + lane + 32 * i];
+                S[i] *= g;
+                a[i & 1] = fmaf(S[i], k[i], a[i & 1]);
+                b[i & 1] = fmaf(S[i], q[i], b[i & 1]);
+            }
+            float sa = a[0] + a[1], sb = b[0] + b[1];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                sa += __shfl_xor_sync(0xffffffffu, sa, o);
+                sb += __shfl_xor_sync(0xffffffffu, sb, o);
+            }
+            const float u = beta * (v - sa);
+#pragma unroll
+            for (int i = 0; i < R; ++i) S[i] = fmaf(k[i], u, S[i]);
+            if (live && lane == 0) p.out[((size_t)(rbase + t) * p.heads + head) * e + c] = fmaf(u, kq, sb);
+        }
+        __syncthreads();                                        // the chunk's buffer may be written again
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < R; ++i)
+            if (lane + 32 * i < d) st[lane + 32 * i] = S[i];
+    }
 }
 
 }  // namespace kb
@@ -280,9 +339,11 @@ extern "C" int kb_delta_scan(float* out, float* scratch, const void* src, int in
 #undef KB_DELTA_PREP
     dim3 grid(entries, heads, (e + DC - 1) / DC);
     const int need = (d + 31) / 32;
-    if (need <= 1) delta_scan_kernel<1><<<grid, DC * 32, 0, s>>>(p);
-    else if (need <= 2) delta_scan_kernel<2><<<grid, DC * 32, 0, s>>>(p);
-    else if (need <= 4) delta_scan_kernel<4><<<grid, DC * 32, 0, s>>>(p);
-    else delta_scan_kernel<DELTA_R><<<grid, DC * 32, 0, s>>>(p);
+#define KB_DELTA_SCAN(R, CH) delta_scan_kernel<R, CH><<<grid, DC * 32, (size_t)2 * CH * (2 * R * 32 + 8) * sizeof(float), s>>>(p)
+    if (need <= 1) KB_DELTA_SCAN(1, 16);
+    else if (need <= 2) KB_DELTA_SCAN(2, 16);
+    else if (need <= 4) KB_DELTA_SCAN(4, 16);
+    else KB_DELTA_SCAN(DELTA_R, 8);
+#undef KB_DELTA_SCAN
     return check_launch("delta scan");
 }
