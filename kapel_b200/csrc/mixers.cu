@@ -17,7 +17,8 @@
 //                    written as the row's line of a cache with one kv head.
 //  head_linear       y[r, h, :] = x[r, h, :] . M[h] for a matrix a head ([heads, n_in, n_out]); optionally
 //                    a rotated copy of further components of x behind the product (the rotated part
-//                    of a latent query), or sigmoid(gate) on the result.
+//                    of a latent query), or sigmoid(gate) on the result. In 32-bit by FMA; with bfloat16
+//                    matrices stored the other way round, on tensor cores (`head_linear_mma`).
 //
 // Sums, norms, rotations and the gates are 32-bit.
 #include "common.cuh"
@@ -281,6 +282,101 @@ head_linear_kernel(T* __restrict__ y, int y_row, int y_head, const Src<TX> x, in
         }
 }
 
+// The same product on tensor cores (mma.sync m16n8k16, bfloat16 in, 32-bit sums) with the matrices stored
+// the other way round, mt [heads, n_out, n_in] (a column of M[h] lies together, as the B operand wants it).
+// One block = 64 rows x one head x 64 columns, four warps of 16 rows; the inner dimension 32 at a time through
+// shared memory (the inputs rounded to bfloat16 there). Any sizes: what lies beyond an edge is zero.
+constexpr int HM_ROWS = 64;
+constexpr int HM_COLS = 64;
+constexpr int HM_K = 32;
+constexpr int HM_LD = HM_K + 8;
+template <typename TX>
+__global__ void __launch_bounds__(128)
+head_linear_mma_kernel(bf16* __restrict__ y, int y_row, int y_head, const Src<TX> x, int x_row, int x_head, int x_off,
+                       const bf16* __restrict__ mt, int n_in, int n_out, int rows, int heads,
+                       int tail_off, int tail, const float2* __restrict__ cos_sin,
+                       const Src<float> gate, int g_row, int g_off) {
+    __shared__ __align__(16) bf16 sa[HM_ROWS * HM_LD];
+    __shared__ __align__(16) bf16 sb[HM_COLS * HM_LD];
+    const int rbase = blockIdx.x * HM_ROWS, h = blockIdx.y, cbase = blockIdx.z * HM_COLS;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, t4 = lane & 3;
+    float acc[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    const bool wide = n_in % 8 == 0 && ((uintptr_t)mt & 15) == 0;
+    for (int k0 = 0; k0 < n_in; k0 += HM_K) {
+        for (int idx = tid; idx < HM_ROWS * HM_K; idx += 128) {
+            const int r = idx / HM_K, k = idx - r * HM_K;
+            float v = 0.f;
+            if (rbase + r < rows && k0 + k < n_in) v = x.at((size_t)(rbase + r) * x_row + (size_t)h * x_head + x_off + k0 + k);
+            sa[r * HM_LD + k] = __float2bfloat16_rn(v);
+        }
+        if (wide) {
+            for (int idx = tid; idx < HM_COLS * (HM_K / 8); idx += 128) {
+                const int n = idx / (HM_K / 8), v = idx - n * (HM_K / 8);
+                uint4 val = make_uint4(0u, 0u, 0u, 0u);
+                if (cbase + n < n_out && k0 + v * 8 < n_in)
+                    val = *reinterpret_cast<const uint4*>(mt + ((size_t)h * n_out + cbase + n) * n_in + k0 + v * 8);
+                *reinterpret_cast<uint4*>(sb + n * HM_LD + v * 8) = val;
+            }
+        } else {
+            for (int idx = tid; idx < HM_COLS * HM_K; idx += 128) {
+                const int n = idx / HM_K, k = idx - n * HM_K;
+                sb[n * HM_LD + k] = (cbase + n < n_out && k0 + k < n_in) ? mt[((size_t)h * n_out + cbase + n) * n_in + k0 + k] : __float2bfloat16_rn(0.f);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < HM_K; ks += 16) {
+            const bf16* pa = sa + (warp * 16 + gid) * HM_LD + ks + 2 * t4;
+            const uint32_t a0 = *reinterpret_cast<const uint32_t*>(pa), a1 = *reinterpret_cast<const uint32_t*>(pa + 8 * HM_LD);
+            const uint32_t a2 = *reinterpret_cast<const uint32_t*>(pa + 8), a3 = *reinterpret_cast<const uint32_t*>(pa + 8 * HM_LD + 8);
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                const bf16* pb = sb + (nt * 8 + gid) * HM_LD + ks + 2 * t4;
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(pb), b1 = *reinterpret_cast<const uint32_t*>(pb + 8);
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(acc[nt][0]), "+f"(acc[nt][1]), "+f"(acc[nt][2]), "+f"(acc[nt][3])
+                             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = rbase + warp * 16 + gid + 8 * (i >> 1), c = cbase + nt * 8 + 2 * t4 + (i & 1);
+            if (r >= rows || c >= n_out) continue;
+            float v = acc[nt][i];
+            if (gate.p != nullptr) {
+                const float z = gate.at((size_t)r * g_row + g_off + (size_t)h * n_out + c);
+                v *= 1.f / (1.f + expf(-z));
+            }
+            y[(size_t)r * y_row + (size_t)h * y_head + c] = __float2bfloat16_rn(v);
+        }
+    }
+    if (blockIdx.z != 0) return;
+    const int nr = min(HM_ROWS, rows - rbase);
+    const int half = tail >> 1;
+    for (int idx = tid; idx < nr * half; idx += 128) {          // behind the product: `tail` further components of x, rotated
+        const int t = idx / half, i = idx - t * half;
+        const size_t at = (size_t)(rbase + t) * x_row + (size_t)h * x_head + tail_off;
+        float a = x.at(at + i), b = x.at(at + i + half);
+        rope_rotate(a, b, cos_sin[(size_t)(rbase + t) * half + i]);
+        bf16* dst = y + (size_t)(rbase + t) * y_row + (size_t)h * y_head + n_out;
+        dst[i] = __float2bfloat16_rn(a);
+        dst[i + half] = __float2bfloat16_rn(b);
+    }
+    if (h == heads - 1) {                                       // a row wider than its heads ends in zeros
+        const int pad = y_row - heads * y_head;
+        for (int idx = tid; idx < nr * pad; idx += 128) {
+            const int t = idx / pad, i = idx - t * pad;
+            y[(size_t)(rbase + t) * y_row + heads * y_head + i] = __float2bfloat16_rn(0.f);
+        }
+    }
+}
+
 __global__ void entry_ranges_clear_kernel(int entries, int* __restrict__ start, int* __restrict__ end) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < entries) {                                      // an entry without rows keeps the empty range
@@ -502,4 +598,31 @@ extern "C" int kb_head_linear(void* y, int dt, int y_row, int y_head, const void
     }
 #undef KB_HL
     return check_launch("head_linear");
+}
+
+// As kb_head_linear with bfloat16 matrices stored [heads, n_out, n_in], on tensor cores; y is bfloat16.
+extern "C" int kb_head_linear_mma(void* y, int y_row, int y_head, const void* x, int x_dt, int x_splits, long long x_split_stride,
+                                  int x_row, int x_head, int x_off, const void* mt, int n_in, int n_out, int rows, int heads,
+                                  int tail_off, int tail, const float* cos_sin, const float* gate, int g_splits,
+                                  long long g_split_stride, int g_row, int g_off, void* stream) {
+    KB_REQUIRE(rows >= 0 && heads > 0 && n_in > 0 && n_out > 0, "head_linear_mma: rows %d, heads %d, sizes %d -> %d", rows, heads, n_in, n_out);
+    KB_REQUIRE(tail >= 0 && tail % 2 == 0 && (tail == 0 || cos_sin != nullptr), "head_linear_mma: %d rotated components (even, with a table)", tail);
+    KB_REQUIRE(y_head >= n_out + tail && y_row >= heads * y_head, "head_linear_mma: output rows of %d, heads of %d for %d + %d values", y_row, y_head, n_out, tail);
+    KB_REQUIRE(x_off >= 0 && x_off + n_in <= x_head && (tail == 0 || (tail_off >= 0 && tail_off + tail <= x_head)) && x_row >= heads * x_head,
+               "head_linear_mma: input rows of %d, heads of %d, columns %d.. and %d..", x_row, x_head, x_off, tail_off);
+    KB_REQUIRE(x_splits >= 1 && (x_splits == 1 || x_split_stride >= (long long)rows * x_row), "head_linear_mma: %d slices %lld apart", x_splits, x_split_stride);
+    KB_REQUIRE(gate == nullptr || (g_splits >= 1 && g_off >= 0 && g_off + heads * n_out <= g_row), "head_linear_mma: gate columns %d.. of a row of %d", g_off, g_row);
+    KB_REQUIRE(heads <= 65535 && (n_out + HM_COLS - 1) / HM_COLS <= 65535, "head_linear_mma: too many heads or columns for one launch");
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid((rows + HM_ROWS - 1) / HM_ROWS, heads, (n_out + HM_COLS - 1) / HM_COLS);
+    const Src<float> g{gate, gate ? g_splits : 1, (size_t)g_split_stride};
+    if (x_dt == KB_DT_F32)
+        head_linear_mma_kernel<float><<<grid, 128, 0, s>>>((bf16*)y, y_row, y_head, Src<float>{(const float*)x, x_splits, (size_t)x_split_stride}, x_row, x_head,
+                                                          x_off, (const bf16*)mt, n_in, n_out, rows, heads, tail_off, tail, (const float2*)cos_sin, g, g_row, g_off);
+    else if (x_dt == KB_DT_BF16)
+        head_linear_mma_kernel<bf16><<<grid, 128, 0, s>>>((bf16*)y, y_row, y_head, Src<bf16>{(const bf16*)x, x_splits, (size_t)x_split_stride}, x_row, x_head,
+                                                         x_off, (const bf16*)mt, n_in, n_out, rows, heads, tail_off, tail, (const float2*)cos_sin, g, g_row, g_off);
+    else return fail("head_linear_mma: dtype code %d is not known", x_dt);
+    return check_launch("head_linear_mma");
 }

@@ -886,18 +886,19 @@ def latent_append(stacked, q_off: int, kv_off: int, q_rank: int, kv_rank: int, r
 
 
 def head_linear(x, heads: int, x_head: int, x_off: int, m: torch.Tensor, y_head: Optional[int] = None, tail_off: int = 0,
-                tail: int = 0, cos_sin=None, gate=None, g_off: int = 0, pad_to: int = 0) -> torch.Tensor:
+                tail: int = 0, cos_sin=None, gate=None, g_off: int = 0, pad_to: int = 0, transposed: bool = False) -> torch.Tensor:
     """y[r, h, :n_out] = x[r, h, x_off : x_off + n_in] . m[h] for `m` [heads, n_in, n_out] (its dtype is
     the output's); `x` [rows, heads * x_head] is a tensor or a SplitSum. With `tail`, the components
     x[r, h, tail_off : tail_off + tail] follow the product in y, turned by `cos_sin` [rows, tail/2, 2].
     With `gate` (a float32 stacked product, tensor or SplitSum) the result is multiplied by the sigmoid
     of its columns g_off + h * n_out ... The result is [rows, heads * y_head] (y_head defaults to
-    n_out + tail), or [rows, pad_to] with zeros behind the heads."""
+    n_out + tail), or [rows, pad_to] with zeros behind the heads. With `transposed`, `m` is bfloat16
+    [heads, n_out, n_in] and the product runs on tensor cores."""
     src, x_dt, splits, stride, rows, x_row = _stacked(x, "head_linear input")
-    _need(m, "head_linear matrices")
+    _need(m, "head_linear matrices", torch.bfloat16 if transposed else None)
     if m.dim() != 3 or m.shape[0] != heads:
         raise KernelError(f"head_linear: matrices of {tuple(m.shape)} for {heads} heads")
-    n_in, n_out = int(m.shape[1]), int(m.shape[2])
+    n_in, n_out = (int(m.shape[2]), int(m.shape[1])) if transposed else (int(m.shape[1]), int(m.shape[2]))
     y_head = int(y_head) if y_head is not None else n_out + int(tail)
     y_row = max(int(pad_to), heads * y_head)
     if tail:
@@ -908,6 +909,12 @@ def head_linear(x, heads: int, x_head: int, x_off: int, m: torch.Tensor, y_head:
         if g_dt != F32 or g_rows != rows:
             raise KernelError("head_linear: the gate must be a float32 product of as many rows")
     y = _fresh((rows, y_row), m.dtype, src.device)
+    if transposed:
+        _check(library().kb_head_linear_mma(
+            _ptr(y), y_row, y_head, _ptr(src), x_dt, splits, ctypes.c_longlong(stride), x_row, int(x_head), int(x_off), _ptr(m), n_in, n_out,
+            rows, int(heads), int(tail_off), int(tail), _ptr(cos_sin if tail else None), _ptr(g_src), int(g_splits),
+            ctypes.c_longlong(g_stride), int(g_row), int(g_off), _stream()))
+        return y
     _check(library().kb_head_linear(
         _ptr(y), _dt(m, "head_linear matrices"), y_row, y_head, _ptr(src), x_dt, splits, ctypes.c_longlong(stride), x_row, int(x_head),
         int(x_off), _ptr(m), n_in, n_out, rows, int(heads), int(tail_off), int(tail), _ptr(cos_sin if tail else None), _ptr(g_src),

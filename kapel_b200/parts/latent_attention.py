@@ -60,9 +60,13 @@ class LatentAttention(Part):
         self.w_uq = pad_columns(ctx, matrix_named(ctx, tensors, w["uq"]))           # the append kernel writes the latent this wide
         self.w_o = pad_columns(ctx, matrix_named(ctx, tensors, w["o"]))
         dev = ctx.device
-        # a matrix a head, [heads, in, out]: uk as it is stored (rows are a head's plain components), uv turned
-        self.m_uk = tensors[w["uk"]].to(dev).to(ctx.dtype).view(H, s.head_dim, s.kv_rank).contiguous()
-        self.m_uv = tensors[w["uv"]].to(dev).to(ctx.dtype).view(H, s.v_head_dim, s.kv_rank).transpose(1, 2).contiguous()
+        # a matrix a head. In 32-bit [heads, in, out] for the FMA kernel: uk as it is stored (rows are a head's plain
+        # components), uv turned. In bfloat16 [heads, out, in] for the tensor-core kernel: uk turned, uv as it is stored.
+        uk = tensors[w["uk"]].to(dev).to(ctx.dtype).view(H, s.head_dim, s.kv_rank)
+        uv = tensors[w["uv"]].to(dev).to(ctx.dtype).view(H, s.v_head_dim, s.kv_rank)
+        self.turned = not ctx.is_f32
+        self.m_uk = (uk.transpose(1, 2) if self.turned else uk).contiguous()
+        self.m_uv = (uv if self.turned else uv.transpose(1, 2)).contiguous()
         norm = lambda n: (tensors[n].to(dev).float() if ctx.is_f32 else tensors[n].to(dev).contiguous())
         self.norm_q, self.norm_kv = norm(w["dq_norm"]), norm(w["dkv_norm"])
         if self.norm_q.dtype != self.norm_kv.dtype:
@@ -83,7 +87,7 @@ class LatentAttention(Part):
         c_q = K.latent_append(stacked, 0, s.q_rank, s.q_rank, s.kv_rank, r, self.norm_q, self.norm_kv, s.eps,
                               cos_sin, group.lines, k_table, cache.owns, ctx.dtype, pad_to=self.w_uq.shape[1])
         q = linear(ctx, c_q, self.w_uq, out_dtype=torch.float32, keep_split=True)
-        q_lat = K.head_linear(q, H, d + r, 0, self.m_uk, y_head=s.kv_rank + r, tail_off=d, tail=r, cos_sin=cos_sin)
+        q_lat = K.head_linear(q, H, d + r, 0, self.m_uk, y_head=s.kv_rank + r, tail_off=d, tail=r, cos_sin=cos_sin, transposed=self.turned)
         if K.latent_attention_mma_takes(q_lat.dtype, s.kv_rank + r, s.kv_rank):
             y = K.latent_attention_mma(q_lat.view(-1, H, s.kv_rank + r), k_table, group.block_table, batch.row_count, batch.entry_ranges(),
                                        batch.entries, batch.longest_portion(), ctx.page_size, s.scale, batch.attention_slots(None),
@@ -93,5 +97,5 @@ class LatentAttention(Part):
                                        batch.row_count, ctx.page_size, None, s.scale, None, batch.attention_slots(None),
                                        sinks=self.sinks, value_dim=s.kv_rank)
         o = K.head_linear(y.view(-1, H * s.kv_rank), H, s.kv_rank, 0, self.m_uv, gate=stacked if s.gated else None,
-                          g_off=s.q_rank + s.kv_rank + r, pad_to=product_width(ctx, H * s.v_head_dim))
+                          g_off=s.q_rank + s.kv_rank + r, pad_to=product_width(ctx, H * s.v_head_dim), transposed=self.turned)
         return linear(ctx, o, self.w_o, keep_split=True)
