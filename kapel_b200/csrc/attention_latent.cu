@@ -6,10 +6,10 @@
 // fetches: one block = up to 64 rows of one request (64 / heads tokens, or one token and a slice of
 // 64 heads) x one chunk of ATT_CHUNK keys, the same chunks, slot numbers, partial sums and merge as the
 // row-wise kernel (`combine_kernel`, which also adds the sink's term), so the two kernels are
-// interchangeable. Within a chunk the keys come 32 at a time into shared memory (16-byte loads through
-// the block table); eight warps: four groups of 16 rows, and for each group two warps that each own half
+// interchangeable. Within a chunk the keys come 32 at a time into shared memory (16-byte asynchronous copies
+// through the block table, the next 32 while these are multiplied); eight warps: four groups of 16 rows, and for each group two warps that each own half
 // of the value's columns. Both compute the group's 16 x 32 scores (Q from shared memory as the A
-// operand, the keys' lines as the B operand: a line is a column of K^T), take the running maximum and
+// operand, the keys' lines as the B operand: a line is a column of K^T; both by ldmatrix), take the running maximum and
 // the weights in 32-bit, and turn the weights into the A operand of the second product in registers;
 // the lines, now as rows of V, come as its B operand by ldmatrix with a transpose. Scores, maxima,
 // sums and the output accumulate in 32-bit. A key is seen by a row when it lies before the row's
@@ -42,9 +42,9 @@ latent_mma_kernel(const AttParams p, const int* __restrict__ entry_start, const 
     const int d = p.d, dv = p.dv, H = p.hq;
     const int ld = d + 8;                                       // elements between rows in shared memory: 16-byte rows, banks spread
     bf16* sq = reinterpret_cast<bf16*>(lm_smem);                // [LM_ROWS][ld]
-    bf16* sk = sq + (size_t)LM_ROWS * ld;                       // [LM_KEYS][ld]
-    int* sline = reinterpret_cast<int*>(sk + (size_t)LM_KEYS * ld);     // [LM_KEYS]
-    int* scount = sline + LM_KEYS;                              // [LM_ROWS]: the count of each row's token, 0 for a row of no token
+    bf16* sk = sq + (size_t)LM_ROWS * ld;                       // [2][LM_KEYS][ld]
+    int* sline = reinterpret_cast<int*>(sk + (size_t)2 * LM_KEYS * ld);  // [2][LM_KEYS]
+    int* scount = sline + 2 * LM_KEYS;                          // [LM_ROWS]: the count of each row's token, 0 for a row of no token
 
     const int entry = blockIdx.y, z = blockIdx.z;
     const int tile = blockIdx.x / head_slices, hslice = blockIdx.x - tile * head_slices;
@@ -88,45 +88,78 @@ latent_mma_kernel(const AttParams p, const int* __restrict__ entry_start, const 
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
     const bf16* kt = static_cast<const bf16*>(p.k_table);
-    for (int k0 = lo; k0 < hi; k0 += LM_KEYS) {
-        if (tid < LM_KEYS) {
-            const int pos = k0 + tid;
+    // The keys of a step come by asynchronous copies, the next step's while this one's are multiplied: two buffers.
+    auto fetch = [&](int k0, int buf) {
+        bf16* dst = sk + (size_t)buf * LM_KEYS * ld;
+        for (int idx = tid; idx < LM_KEYS * nvec; idx += LM_THREADS) {
+            const int key = idx / nvec, v = idx - key * nvec;
+            const int pos = k0 + key;
             int line = -1;
             if (pos < hi) {
                 const int lp = pos / p.page_size;
                 const int page = lp < p.table_width ? p.block_table[(size_t)entry * p.table_width + lp] : -1;
                 if (page >= 0 && page < p.n_pages) line = page * p.page_size + pos % p.page_size;
             }
-            sline[tid] = line;
+            if (v == 0) sline[buf * LM_KEYS + key] = line;
+            bf16* to = dst + (size_t)key * ld + v * 8;
+            if (line >= 0) {
+                const uint32_t to32 = (uint32_t)__cvta_generic_to_shared(to);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to32), "l"(kt + kv_row(line, 0, 1, p.page_size) * d + v * 8) : "memory");
+            } else {
+                *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (lo < hi) fetch(lo, 0);
+    int turn = 0;
+    for (int k0 = lo; k0 < hi; k0 += LM_KEYS, turn ^= 1) {
+        if (k0 + LM_KEYS < hi) {
+            fetch(k0 + LM_KEYS, turn ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
-        for (int idx = tid; idx < LM_KEYS * nvec; idx += LM_THREADS) {
-            const int key = idx / nvec, v = idx - key * nvec;
-            const int line = sline[key];
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (line >= 0) val = *reinterpret_cast<const uint4*>(kt + kv_row(line, 0, 1, p.page_size) * d + v * 8);
-            *reinterpret_cast<uint4*>(sk + (size_t)key * ld + v * 8) = val;
-        }
-        __syncthreads();
+        const bf16* skb = sk + (size_t)turn * LM_KEYS * ld;
+        const int* slineb = sline + turn * LM_KEYS;
 
         // ---- scores of 16 rows x 32 keys
         float s[4][4];
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-        const bf16* qa = sq + (size_t)row_a * ld + 2 * t4;
-        const bf16* qb = sq + (size_t)row_b * ld + 2 * t4;
-        for (int kk = 0; kk < d; kk += 16) {
-            uint32_t a[4];
-            a[0] = *reinterpret_cast<const uint32_t*>(qa + kk);
-            a[1] = *reinterpret_cast<const uint32_t*>(qb + kk);
-            a[2] = *reinterpret_cast<const uint32_t*>(qa + kk + 8);
-            a[3] = *reinterpret_cast<const uint32_t*>(qb + kk + 8);
+        // operands by ldmatrix: Q's 16 x 16 piece as four 8 x 8 matrices in the A operand's order; the lines of two
+        // 8-key tiles (keys are the matrices' rows, so no transpose) as b0, b1 of one tile and b0, b1 of the next
+        const uint32_t qaddr = (uint32_t)__cvta_generic_to_shared(sq + (size_t)(group * 16 + (lane & 15)) * ld + (lane >> 4) * 8);
+        const uint32_t kaddr = (uint32_t)__cvta_generic_to_shared(skb + (size_t)((lane >> 4) * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8);
+        // two sets of sums taking the 16-component steps in turn: eight chains of products in flight instead of four
+        float s2[4][4];
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const bf16* kp = sk + (size_t)(nt * 8 + gid) * ld + kk + 2 * t4;
-                mma_bf16(s[nt], a, *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+        for (int nt = 0; nt < 4; ++nt) s2[nt][0] = s2[nt][1] = s2[nt][2] = s2[nt][3] = 0.f;
+        for (int kk = 0; kk < d; kk += 32) {
+            uint32_t a[4], b[4], c[4];
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(qaddr + kk * 2));
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(kaddr + kk * 2));
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(kaddr + (16 * ld + kk) * 2));
+            mma_bf16(s[0], a, b[0], b[1]);
+            mma_bf16(s[1], a, b[2], b[3]);
+            mma_bf16(s[2], a, c[0], c[1]);
+            mma_bf16(s[3], a, c[2], c[3]);
+            if (kk + 16 < d) {
+                uint32_t a2[4], b2[4], c2[4];
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a2[0]), "=r"(a2[1]), "=r"(a2[2]), "=r"(a2[3]) : "r"(qaddr + (kk + 16) * 2));
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(b2[0]), "=r"(b2[1]), "=r"(b2[2]), "=r"(b2[3]) : "r"(kaddr + (kk + 16) * 2));
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(c2[0]), "=r"(c2[1]), "=r"(c2[2]), "=r"(c2[3]) : "r"(kaddr + (16 * ld + kk + 16) * 2));
+                mma_bf16(s2[0], a2, b2[0], b2[1]);
+                mma_bf16(s2[1], a2, b2[2], b2[3]);
+                mma_bf16(s2[2], a2, c2[0], c2[1]);
+                mma_bf16(s2[3], a2, c2[2], c2[3]);
             }
         }
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[nt][c] += s2[nt][c];
         // ---- mask, running maximum, weights
         float top_a = m_a, top_b = m_b;
 #pragma unroll
@@ -134,7 +167,7 @@ latent_mma_kernel(const AttParams p, const int* __restrict__ entry_start, const 
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int key = k0 + nt * 8 + 2 * t4 + (c & 1);
-                const bool seen = key < ((c & 2) ? count_b : count_a) && sline[nt * 8 + 2 * t4 + (c & 1)] >= 0;
+                const bool seen = key < ((c & 2) ? count_b : count_a) && slineb[nt * 8 + 2 * t4 + (c & 1)] >= 0;
                 s[nt][c] = seen ? s[nt][c] * p.scale : -INFINITY;
                 if (c & 2) top_b = fmaxf(top_b, s[nt][c]);
                 else top_a = fmaxf(top_a, s[nt][c]);
@@ -179,7 +212,7 @@ latent_mma_kernel(const AttParams p, const int* __restrict__ entry_start, const 
             a[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
             a[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
             a[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
-            const uint32_t row_addr = (uint32_t)__cvta_generic_to_shared(sk + (size_t)(ks * 16 + (lane & 15)) * ld + col0);
+            const uint32_t row_addr = (uint32_t)__cvta_generic_to_shared(skb + (size_t)(ks * 16 + (lane & 15)) * ld + col0);
 #pragma unroll
             for (int j = 0; j < LM_MAX_NT; ++j) {
                 if (j < ntiles) {
@@ -189,7 +222,7 @@ latent_mma_kernel(const AttParams p, const int* __restrict__ entry_start, const 
                 }
             }
         }
-        __syncthreads();                                        // the keys' buffer is written again
+        __syncthreads();                                        // this buffer is written again by the step after the next
     }
 
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
@@ -250,7 +283,7 @@ using namespace kb;
 // halves of whole 8-column tiles a warp can hold.
 extern "C" int kb_latent_attention_mma_takes(int d, int dv) {
     if (d <= 0 || dv <= 0 || dv > d || d % 16 || dv % 16 || dv > 2 * 8 * LM_MAX_NT) return 0;
-    const size_t smem = ((size_t)LM_ROWS + LM_KEYS) * (d + 8) * sizeof(bf16) + (LM_KEYS + LM_ROWS) * sizeof(int);
+    const size_t smem = ((size_t)LM_ROWS + 2 * LM_KEYS) * (d + 8) * sizeof(bf16) + (2 * LM_KEYS + LM_ROWS) * sizeof(int);
     return smem <= 200 * 1024 ? 1 : 0;
 }
 
@@ -278,7 +311,7 @@ extern "C" int kb_latent_attention_mma(void* out, const void* q, const void* tab
     const int tokens_per_tile = LM_ROWS / heads_per_tile;
     const long long tiles = (long long)((longest + tokens_per_tile - 1) / tokens_per_tile) * head_slices;
     KB_REQUIRE(tiles <= 0x7fffffffll && entries <= 65535, "latent_attention_mma: too many tiles or requests for one launch");
-    const size_t smem = ((size_t)LM_ROWS + LM_KEYS) * (d + 8) * sizeof(bf16) + (LM_KEYS + LM_ROWS) * sizeof(int);
+    const size_t smem = ((size_t)LM_ROWS + 2 * LM_KEYS) * (d + 8) * sizeof(bf16) + (2 * LM_KEYS + LM_ROWS) * sizeof(int);
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(latent_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
