@@ -32,7 +32,7 @@ extern "C" int kb_paged_attention_rows(void* out, const void* q, const void* k_t
     p.n_pages = n_pages; p.dv = dv; p.vec = (d % (dt == KB_DT_F32 ? 4 : 8)) == 0 && ((uintptr_t)k_table & 15) == 0; p.window = window; p.keep = window > 0 ? keep : 0;
     p.keep_slots = p.keep > 0 ? (p.keep + ATT_CHUNK - 1) / ATT_CHUNK : 0;
     KB_REQUIRE(slots > p.keep_slots, "paged_attention: %d slots of which %d are the kept first keys'", slots, p.keep_slots);
-    p.slots = slots; p.scale = scale; p.cap = cap; p.v_stride = v_stride; p.sinks = sinks;
+    p.slots = slots; p.chunk = ATT_CHUNK; p.scale = scale; p.cap = cap; p.v_stride = v_stride; p.sinks = sinks;
     cudaStream_t s = (cudaStream_t)stream;
     if (dt == KB_DT_F32) return rows_f32(p, s, slots > 1);
     if (dt == KB_DT_BF16) return rows_bf16(p, s, slots > 1);

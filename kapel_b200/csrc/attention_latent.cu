@@ -4,9 +4,9 @@
 // The cache has one kv head; a line holds d components, of which the first dv are the value. Every
 // query head of a token reads the same lines, so a tile of 64 (token, head) rows shares each key it
 // fetches: one block = up to 64 rows of one request (64 / heads tokens, or one token and a slice of
-// 64 heads) x one chunk of ATT_CHUNK keys, the same chunks, slot numbers, partial sums and merge as the
-// row-wise kernel (`combine_kernel`, which also adds the sink's term), so the two kernels are
-// interchangeable. Within a chunk the keys come 32 at a time into shared memory (16-byte asynchronous copies
+// 64 heads) x one chunk of keys (a launch's choice: the row-wise kernel's 256 for single tokens, where
+// many blocks must share a long history; longer for prompts, which have tiles enough), with the slot
+// numbers, partial sums and merge of the row-wise kernel (`combine_kernel`, which also adds the sink's term). Within a chunk the keys come 32 at a time into shared memory (16-byte asynchronous copies
 // through the block table, the next 32 while these are multiplied); eight warps: four groups of 16 rows, and for each group two warps that each own half
 // of the value's columns. Both compute the group's 16 x 32 scores (Q from shared memory as the A
 // operand, the keys' lines as the B operand: a line is a column of K^T; both by ldmatrix), take the running maximum and
@@ -47,7 +47,9 @@ latent_mma_kernel(const AttParams p, const int* __restrict__ entry_start, const 
     int* scount = sline + 2 * LM_KEYS;                          // [LM_ROWS]: the count of each row's token, 0 for a row of no token
 
     const int entry = blockIdx.y, z = blockIdx.z;
-    const int tile = blockIdx.x / head_slices, hslice = blockIdx.x - tile * head_slices;
+    // the last tiles of a request see the most keys: they go first, so that the short ones fill the launch's end
+    const int flipped = gridDim.x - 1 - blockIdx.x;
+    const int tile = flipped / head_slices, hslice = flipped - tile * head_slices;
     const int e0 = entry_start[entry], e1 = entry_end[entry];
     const int r0 = e0 + tile * tokens_per_tile;
     if (r0 >= e1) return;
@@ -80,7 +82,7 @@ latent_mma_kernel(const AttParams p, const int* __restrict__ entry_start, const 
     const int row_a = group * 16 + gid, row_b = row_a + 8;      // this thread's two rows of the tile
     const int count_a = scount[row_a], count_b = scount[row_b];
     const int most = p.row_count[r0 + ntok - 1];                // counts rise along a request's rows
-    const int lo = z * ATT_CHUNK, hi = min(most, (z + 1) * ATT_CHUNK);
+    const int lo = z * p.chunk, hi = min(most, (z + 1) * p.chunk);
 
     float o[LM_MAX_NT][4];
 #pragma unroll
@@ -289,11 +291,13 @@ extern "C" int kb_latent_attention_mma_takes(int d, int dv) {
 
 // q [rows, hq, d], table [pages, 1, page_size, d] (a line's first dv components are its value), out [rows, hq, dv]: bfloat16.
 // entry_start / entry_end [entries]: the rows of each request; `longest`: the most rows any request brings.
+// `chunk`: keys a slot holds, `slots` >= ceil(longest count / chunk).
 // scratch: kb_paged_attention_scratch_floats(rows, hq, dv, slots) floats when slots > 1.
 extern "C" int kb_latent_attention_mma(void* out, const void* q, const void* table, const int* block_table, const int* row_count,
                                        const int* entry_start, const int* entry_end, int entries, int longest, int rows, int hq,
-                                       int d, int dv, int page_size, int table_width, int n_pages, int slots, float scale,
+                                       int d, int dv, int page_size, int table_width, int n_pages, int slots, int chunk, float scale,
                                        float* scratch, const float* sinks, void* stream) {
+    KB_REQUIRE(chunk >= LM_KEYS && chunk % LM_KEYS == 0, "latent_attention_mma: chunks of %d keys (a multiple of %d)", chunk, LM_KEYS);
     KB_REQUIRE(rows >= 0 && entries >= 0 && hq > 0 && longest >= 0, "latent_attention_mma: rows %d, requests %d, heads %d, longest %d", rows, entries, hq, longest);
     KB_REQUIRE(kb_latent_attention_mma_takes(d, dv), "latent_attention_mma: lines of %d with values of %d are not taken (multiples of 16, values at most %d)", d, dv, 2 * 8 * LM_MAX_NT);
     KB_REQUIRE(page_size > 0 && table_width > 0 && n_pages > 0, "latent_attention_mma: page_size %d, table width %d, pages %d", page_size, table_width, n_pages);
@@ -305,7 +309,7 @@ extern "C" int kb_latent_attention_mma(void* out, const void* q, const void* tab
     p.q = q; p.k_table = table; p.v_table = table; p.block_table = block_table; p.row_entry = nullptr; p.row_count = row_count;
     p.out = out; p.partial = slots > 1 ? scratch : nullptr; p.rows = rows; p.hq = hq; p.hkv = 1; p.d = d; p.page_size = page_size;
     p.table_width = table_width; p.n_pages = n_pages; p.dv = dv; p.v_stride = d; p.sinks = sinks; p.vec = 1; p.window = 0; p.keep = 0;
-    p.keep_slots = 0; p.slots = slots; p.scale = scale; p.cap = 0.f;
+    p.keep_slots = 0; p.slots = slots; p.chunk = chunk; p.scale = scale; p.cap = 0.f;
     const int heads_per_tile = hq < LM_ROWS ? hq : LM_ROWS;
     const int head_slices = (hq + heads_per_tile - 1) / heads_per_tile;
     const int tokens_per_tile = LM_ROWS / heads_per_tile;

@@ -69,6 +69,7 @@ struct AttParams {
     int keep;                 // with a window: the keys [0, keep) stay visible below it
     int keep_slots;           // ceil(keep / CHUNK) with a window and keep > 0, else 0: the slots of those keys
     int slots;                // chunk slots a row may touch, the kept keys' included
+    int chunk;                // keys a slot holds: ATT_CHUNK for the row-wise kernel (its shared memory is made for that); another kernel may cut longer
     float scale, cap;         // cap 0: none
 };
 
@@ -78,12 +79,12 @@ struct AttParams {
 __device__ __forceinline__ void slot_range(const AttParams& p, int count, int z, int& lo, int& hi) {
     const int first = (p.window > 0 && count > p.window) ? count - p.window : 0;
     if (z < p.keep_slots) {
-        lo = z * ATT_CHUNK;
-        hi = min(min(p.keep, first), (z + 1) * ATT_CHUNK);
+        lo = z * p.chunk;
+        hi = min(min(p.keep, first), (z + 1) * p.chunk);
     } else {
-        const int chunk = first / ATT_CHUNK + (z - p.keep_slots);      // absolute chunk index
-        lo = max(first, chunk * ATT_CHUNK);
-        hi = min(count, (chunk + 1) * ATT_CHUNK);
+        const int chunk = first / p.chunk + (z - p.keep_slots);       // absolute chunk index
+        lo = max(first, chunk * p.chunk);
+        hi = min(count, (chunk + 1) * p.chunk);
     }
 }
 

@@ -250,7 +250,7 @@ def latent_reference(x_q, c, k_rot, uk, uv, sinks, H, d, r, e, scale):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 3e-2)])
 @pytest.mark.parametrize("H,d,r,e,q_rank,kv,T", [(3, 8, 4, 16, 24, 12, 300), (1, 16, 16, 8, 8, 40, 40), (10, 12, 6, 5, 20, 33, 70), (4, 32, 32, 32, 64, 64, 530),
-                                                 (16, 16, 16, 16, 32, 48, 300), (80, 8, 16, 8, 16, 16, 40), (6, 16, 32, 24, 40, 96, 270)])
+                                                 (16, 16, 16, 16, 32, 48, 300), (80, 8, 16, 8, 16, 16, 40), (6, 16, 32, 24, 40, 96, 270), (2, 16, 16, 16, 16, 32, 4500)])
 def test_attention_through_latents_with_a_sink(H, d, r, e, q_rank, kv, T, dtype, tol):
     """The latents' norms, the one rotated key part, the append; queries carried into the latent's space; all heads on
     the one cached line whose first part is the value; the sink in the denominator; values back out through uv with
