@@ -284,8 +284,13 @@ rows_kernel(const AttParams p) {
 }
 
 // out[r, h, :] = sum_z e^(m_z - M) acc_z / sum_z e^(m_z - M) l_z over the slots that held keys of the row.
+// The slots' maxima and sums are read by the block's threads side by side (a slot a thread), the weights
+// e^(m_z - M) left in shared memory; then a thread a component walks the slots with independent loads.
+constexpr int COMBINE_SLOTS = 1024;    // slots whose weights fit shared memory; beyond that they are computed again a component
 template <typename T>
 __global__ void combine_kernel(const AttParams p) {
+    __shared__ float scratch[32];
+    __shared__ float weight[COMBINE_SLOTS];
     const int r = blockIdx.x, h = blockIdx.y;
     const int count = p.row_count[r];
     const int dv = p.dv;
@@ -293,27 +298,36 @@ __global__ void combine_kernel(const AttParams p) {
     if (count <= 0) return;                                // the rows kernel wrote zeros
     const float* base = p.partial + ((size_t)r * p.hq + h) * p.slots * (dv + 2);
     float mx = -INFINITY;
-    for (int z = 0; z < p.slots; ++z) {
+    for (int z = threadIdx.x; z < p.slots; z += blockDim.x) {
         int lo, hi;
         slot_range(p, count, z, lo, hi);
         if (hi > lo) mx = fmaxf(mx, base[(size_t)z * (dv + 2) + dv]);
     }
+    mx = block_max(mx, scratch);
+    if (p.sinks != nullptr) mx = fmaxf(mx, p.sinks[h]);
     float denom = 0.f;
-    if (p.sinks != nullptr) {
-        mx = fmaxf(mx, p.sinks[h]);
-        denom = soft_exp<T>(p.sinks[h] - mx);
-    }
-    for (int z = 0; z < p.slots; ++z) {
+    for (int z = threadIdx.x; z < p.slots; z += blockDim.x) {
         int lo, hi;
         slot_range(p, count, z, lo, hi);
-        if (hi <= lo) continue;
-        const float m = base[(size_t)z * (dv + 2) + dv];
-        denom += (m == -INFINITY ? 0.f : soft_exp<T>(m - mx)) * base[(size_t)z * (dv + 2) + dv + 1];
+        float w = 0.f;
+        if (hi > lo) {
+            const float m = base[(size_t)z * (dv + 2) + dv];
+            w = m == -INFINITY ? 0.f : soft_exp<T>(m - mx);
+            denom += w * base[(size_t)z * (dv + 2) + dv + 1];
+        }
+        if (z < COMBINE_SLOTS) weight[z] = w;
     }
+    denom = block_sum(denom, scratch);                     // (its barriers also publish the weights)
+    if (p.sinks != nullptr) denom += soft_exp<T>(p.sinks[h] - mx);
     const float inv = denom > 0.f ? 1.f / denom : 0.f;
     for (int i = threadIdx.x; i < dv; i += blockDim.x) {
         float acc = 0.f;
-        for (int z = 0; z < p.slots; ++z) {
+        const int known = min(p.slots, COMBINE_SLOTS);
+        for (int z = 0; z < known; ++z) {
+            const float w = weight[z];
+            if (w != 0.f) acc = fmaf(w, base[(size_t)z * (dv + 2) + i], acc);
+        }
+        for (int z = known; z < p.slots; ++z) {
             int lo, hi;
             slot_range(p, count, z, lo, hi);
             if (hi <= lo) continue;

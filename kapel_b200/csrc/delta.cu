@@ -57,7 +57,7 @@ __device__ __forceinline__ float delta_softplus(float x) { return x > 20.f ? x :
 __device__ __forceinline__ float delta_silu(float x) { return x / (1.f + expf(-x)); }
 
 template <typename TS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 delta_prep_kernel(const Src<TS> src, const DeltaParams p) {
     extern __shared__ float act[];                              // [channels]
     const int r = blockIdx.x;
@@ -325,7 +325,7 @@ extern "C" int kb_delta_scan(float* out, float* scratch, const void* src, int in
 #define KB_DELTA_PREP(TS)                                                                                                  \
     do {                                                                                                                   \
         if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        delta_prep_kernel<TS><<<rows, 256, smem, s>>>(Src<TS>{(const TS*)src, splits, (size_t)split_stride}, p);           \
+        delta_prep_kernel<TS><<<rows, rows <= DEPENDENT_ROWS ? 1024 : 256, smem, s>>>(Src<TS>{(const TS*)src, splits, (size_t)split_stride}, p); /* few rows: a channel or two a thread */ \
         if (int err = check_launch("delta prep")) return err;                                                              \
         if (taps > 1) {                                                                                                    \
             delta_history_kernel<TS><<<dim3((unsigned)((channels + 127) / 128), entries), 128, 0, s>>>(                     \

@@ -377,6 +377,70 @@ head_linear_mma_kernel(bf16* __restrict__ y, int y_row, int y_head, const Src<TX
     }
 }
 
+// The same product for a few rows (a decode step): one warp a column of M[h] for all rows. The lanes walk the
+// column's n_in values (they lie together in mt [heads, n_out, n_in]), every row's inputs lie in shared memory;
+// a warp sum a row. 32-bit sums; inputs and matrices as they come (no rounding of the inputs).
+constexpr int HF_ROWS = 16;
+constexpr int HF_WARPS = 8;
+template <typename TX>
+__global__ void __launch_bounds__(HF_WARPS * 32)
+head_linear_few_kernel(bf16* __restrict__ y, int y_row, int y_head, const Src<TX> x, int x_row, int x_head, int x_off,
+                       const bf16* __restrict__ mt, int n_in, int n_out, int rows, int heads,
+                       int tail_off, int tail, const float2* __restrict__ cos_sin,
+                       const Src<float> gate, int g_row, int g_off) {
+    extern __shared__ float xf[];                               // [rows][n_in]
+    const int h = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int idx = tid; idx < rows * n_in; idx += HF_WARPS * 32) {
+        const int t = idx / n_in, i = idx - t * n_in;
+        xf[idx] = x.at((size_t)t * x_row + (size_t)h * x_head + x_off + i);
+    }
+    __syncthreads();
+    const int c = blockIdx.y * HF_WARPS + warp;
+    if (c < n_out) {
+        float acc[HF_ROWS];
+#pragma unroll
+        for (int t = 0; t < HF_ROWS; ++t) acc[t] = 0.f;
+        const bf16* col = mt + ((size_t)h * n_out + c) * n_in;
+        for (int i = lane; i < n_in; i += 32) {
+            const float w = __bfloat162float(col[i]);
+#pragma unroll
+            for (int t = 0; t < HF_ROWS; ++t)
+                if (t < rows) acc[t] = fmaf(xf[t * n_in + i], w, acc[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < HF_ROWS; ++t) {
+            if (t >= rows) continue;
+            float v = warp_sum(acc[t]);
+            if (lane == 0) {
+                if (gate.p != nullptr) {
+                    const float z = gate.at((size_t)t * g_row + g_off + (size_t)h * n_out + c);
+                    v *= 1.f / (1.f + expf(-z));
+                }
+                y[(size_t)t * y_row + (size_t)h * y_head + c] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+    if (blockIdx.y != 0) return;
+    const int half = tail >> 1;
+    for (int idx = tid; idx < rows * half; idx += HF_WARPS * 32) {
+        const int t = idx / half, i = idx - t * half;
+        const size_t at = (size_t)t * x_row + (size_t)h * x_head + tail_off;
+        float a = x.at(at + i), b = x.at(at + i + half);
+        rope_rotate(a, b, cos_sin[(size_t)t * half + i]);
+        bf16* dst = y + (size_t)t * y_row + (size_t)h * y_head + n_out;
+        dst[i] = __float2bfloat16_rn(a);
+        dst[i + half] = __float2bfloat16_rn(b);
+    }
+    if (h == heads - 1) {
+        const int pad = y_row - heads * y_head;
+        for (int idx = tid; idx < rows * pad; idx += HF_WARPS * 32) {
+            const int t = idx / pad, i = idx - t * pad;
+            y[(size_t)t * y_row + heads * y_head + i] = __float2bfloat16_rn(0.f);
+        }
+    }
+}
+
 __global__ void entry_ranges_clear_kernel(int entries, int* __restrict__ start, int* __restrict__ end) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < entries) {                                      // an entry without rows keeps the empty range
@@ -504,7 +568,7 @@ extern "C" int kb_head_norm_rope_append(const void* src, int in_dt, int splits, 
     if (rows == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     void* kt = write_kv ? k_table : nullptr;
-    const int warps = 4;
+    const int warps = rows <= DEPENDENT_ROWS ? 16 : 4;          // few rows: a head vector a warp side by side
     const size_t smem = (size_t)warps * d * sizeof(float);
 #define KB_HNRA(TS, TW, TO)                                                                                              \
     head_norm_rope_append_kernel<TS, TW, TO><<<rows, warps * 32, smem, s>>>(                                                 \
@@ -542,7 +606,7 @@ extern "C" int kb_latent_append(const void* src, int in_dt, int splits, long lon
     cudaStream_t s = (cudaStream_t)stream;
     void* kt = write_kv ? k_table : nullptr;
 #define KB_LA(TS, TW, TO)                                                                                                  \
-    latent_append_kernel<TS, TW, TO><<<rows, 128, 0, s>>>(Src<TS>{(const TS*)src, splits, (size_t)split_stride}, row_width, q_off, \
+    latent_append_kernel<TS, TW, TO><<<rows, rows <= DEPENDENT_ROWS ? 1024 : 128, 0, s>>>(Src<TS>{(const TS*)src, splits, (size_t)split_stride}, row_width, q_off, \
                                                           kv_off, q_rank, kv_rank, rot, (const TW*)wq, (const TW*)wkv, eps,     \
                                                           (const float2*)cos_sin, lines, (TO*)cq_out, cq_stride, (TO*)kt,       \
                                                           table_lines, page_size)
@@ -615,8 +679,20 @@ extern "C" int kb_head_linear_mma(void* y, int y_row, int y_head, const void* x,
     KB_REQUIRE(heads <= 65535 && (n_out + HM_COLS - 1) / HM_COLS <= 65535, "head_linear_mma: too many heads or columns for one launch");
     if (rows == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid((rows + HM_ROWS - 1) / HM_ROWS, heads, (n_out + HM_COLS - 1) / HM_COLS);
     const Src<float> g{gate, gate ? g_splits : 1, (size_t)g_split_stride};
+    const size_t few_smem = (size_t)rows * n_in * sizeof(float);
+    if (rows <= HF_ROWS && few_smem <= 48 * 1024 && (n_out + HF_WARPS - 1) / HF_WARPS <= 65535) {     // a decode step: a warp a column
+        dim3 few(heads, (n_out + HF_WARPS - 1) / HF_WARPS);
+        if (x_dt == KB_DT_F32)
+            head_linear_few_kernel<float><<<few, HF_WARPS * 32, few_smem, s>>>((bf16*)y, y_row, y_head, Src<float>{(const float*)x, x_splits, (size_t)x_split_stride}, x_row,
+                                                                             x_head, x_off, (const bf16*)mt, n_in, n_out, rows, heads, tail_off, tail, (const float2*)cos_sin, g, g_row, g_off);
+        else if (x_dt == KB_DT_BF16)
+            head_linear_few_kernel<bf16><<<few, HF_WARPS * 32, few_smem, s>>>((bf16*)y, y_row, y_head, Src<bf16>{(const bf16*)x, x_splits, (size_t)x_split_stride}, x_row,
+                                                                            x_head, x_off, (const bf16*)mt, n_in, n_out, rows, heads, tail_off, tail, (const float2*)cos_sin, g, g_row, g_off);
+        else return fail("head_linear_mma: dtype code %d is not known", x_dt);
+        return check_launch("head_linear_few");
+    }
+    dim3 grid((rows + HM_ROWS - 1) / HM_ROWS, heads, (n_out + HM_COLS - 1) / HM_COLS);
     if (x_dt == KB_DT_F32)
         head_linear_mma_kernel<float><<<grid, 128, 0, s>>>((bf16*)y, y_row, y_head, Src<float>{(const float*)x, x_splits, (size_t)x_split_stride}, x_row, x_head,
                                                           x_off, (const bf16*)mt, n_in, n_out, rows, heads, tail_off, tail, (const float2*)cos_sin, g, g_row, g_off);

@@ -749,7 +749,8 @@ extern "C" int kb_add_norm(float* residual, const void* branch, int branch_dt, i
     KB_REQUIRE(smem <= 200 * 1024, "add_norm: a row of %d values does not fit the shared memory of a block", width);
     if (rows == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int t = threads_for(width);
+    // few rows (a decode step): latency counts, so a row is spread over as many threads as it has pairs of values
+    const int t = rows <= DEPENDENT_ROWS ? std::min(1024, std::max(128, ((width + 1) / 2 + 31) / 32 * 32)) : threads_for(width);
 #define KB_ADDLN(TB, TW, TH)                                                                                              \
     do {                                                                                                                  \
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_norm_centered_kernel<TB, TW, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \

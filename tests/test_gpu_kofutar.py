@@ -181,7 +181,8 @@ def paged(rng, n_tokens, page_size=16, spare=3):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 5e-6), (torch.bfloat16, 1.5e-2)])
-@pytest.mark.parametrize("hq,hkv,d,dv,rotary", [(4, 2, 16, 16, 8), (6, 2, 16, 8, 16), (1, 1, 32, 40, 0), (3, 3, 10, 6, 4), (8, 1, 64, 64, 32)])
+@pytest.mark.parametrize("hq,hkv,d,dv,rotary", [(4, 2, 16, 16, 8), (6, 2, 16, 8, 16), (1, 1, 32, 40, 0), (3, 3, 10, 6, 4), (8, 1, 64, 64, 32),
+                                                 (4, 2, 48, 48, 16), (2, 1, 96, 96, 96), (2, 2, 80, 80, 40), (2, 2, 128, 128, 64)])
 def test_attention_with_head_norms_rotation_and_append(hq, hkv, d, dv, rotary, dtype, tol):
     """Every head's query and key normed with one shared weight, then turned; keys and values land in shuffled
     pages; the row-wise kernel (and, where it applies, the tensor-core kernel) over them gives the plain heads."""
@@ -287,6 +288,9 @@ def test_attention_through_latents_with_a_sink(H, d, r, e, q_rank, kv, T, dtype,
         turned = K.head_linear(dev(q.reshape(T, -1)), H, d + r, 0, dev(uk.reshape(H, d, kv).transpose(0, 2, 1), dtype), y_head=kv + r,
                                tail_off=d, tail=r, cos_sin=cs, transposed=True)
         assert rel_err(turned.float().cpu().numpy(), q_lat.float().cpu().numpy()) < 1e-2
+        few = K.head_linear(dev(q.reshape(T, -1)[:5]), H, d + r, 0, dev(uk.reshape(H, d, kv).transpose(0, 2, 1), dtype), y_head=kv + r,
+                            tail_off=d, tail=r, cos_sin=cs[:5].contiguous(), transposed=True)          # a few rows: a warp a column
+        assert rel_err(few.float().cpu().numpy(), turned[:5].float().cpu().numpy()) < 1e-2
         q_lat = turned
     count, entry = dev(pos + 1, torch.int32), torch.zeros(T, dtype=torch.int32, device="cuda")
     bt = dev(np.concatenate([pages, [-1]])[None, :], torch.int32)
@@ -314,6 +318,9 @@ def test_attention_through_latents_with_a_sink(H, d, r, e, q_rank, kv, T, dtype,
         turned = K.head_linear(y.view(T, H * kv), H, kv, 0, dev(uv.reshape(H, e, kv), dtype), gate=dev(stacked), g_off=q_rank + kv + r,
                                pad_to=H * e + 3, transposed=True)
         assert float(turned[:, H * e :].abs().max()) == 0.0 and rel_err(turned.float().cpu().numpy(), o.float().cpu().numpy()) < 1e-2
+        few = K.head_linear(y.view(T, H * kv)[:3].contiguous(), H, kv, 0, dev(uv.reshape(H, e, kv), dtype), gate=dev(stacked[:3]),
+                            g_off=q_rank + kv + r, pad_to=H * e + 3, transposed=True)
+        assert float(few[:, H * e :].abs().max()) == 0.0 and rel_err(few.float().cpu().numpy(), turned[:3].float().cpu().numpy()) < 1e-2
         o = turned
     want = latent_reference(q_turned, rd(want_c) if dtype == torch.bfloat16 else want_c, rd(want_kr) if dtype == torch.bfloat16 else want_kr,
                             uk, uv, sinks, H, d, r, e, 0.27)
