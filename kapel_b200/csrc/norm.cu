@@ -539,10 +539,33 @@ __global__ void add_norm_centered_kernel(float* __restrict__ residual, const Src
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * width;
     float sum = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float b = branch.at(base + i);
-        row[i] = b;
-        sum += b;
+    const int ept = (width + blockDim.x - 1) / blockDim.x;
+    if (ept <= 4 && branch.splits > 1) {
+        // a few values a thread and many slices (a decode step): every slice's loads are asked for side by side,
+        // and added in the slices' order as `Src::at` adds them
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+        for (int sl = 0; sl < branch.splits; ++sl) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = threadIdx.x + e * blockDim.x;
+                if (e < ept && i < width) acc[e] += Elem<TB>::load(branch.p + (size_t)sl * branch.stride + base + i);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = threadIdx.x + e * blockDim.x;
+            if (e < ept && i < width) {
+                row[i] = acc[e];
+                sum += acc[e];
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float b = branch.at(base + i);
+            row[i] = b;
+            sum += b;
+        }
     }
     float mean = 0.f, inv = 1.f;
     if (w_post != nullptr) {
