@@ -15,9 +15,9 @@
 // the step come from the slot's history), unit norms of q and k per head, q.k per kv head, decay and
 // step size per head, all left in 32-bit scratch. `delta_history_kernel`, a thread a channel of a
 // request: the slot's history becomes the last taps - 1 inputs. `delta_scan_kernel`: one block = one
-// request of the step x one head x DC value components, a warp a component, lane l the memory's rows
-// j = l, l + 32, ... of that column in registers. Written with the decayed memory M = g S of a row:
-// a = M.k and b = M.q are reduced side by side (one round of shuffles a row), u = beta (v - a),
+// request of the step x one head x 4, 8 or 16 value components, a warp one, two or four of them, lane l the memory's
+// rows j = l, l + 32, ... of those columns in registers. Written with the decayed memory M = g S of a row:
+// a = M.k and b = M.q of a warp's columns are reduced together (5, 6 or 9 shuffles a row), u = beta (v - a),
 // o = b + u (k.q), S = M + k u. The rows' inputs come into shared memory a chunk of rows at a time by
 // asynchronous copies, the next chunk while this one is walked. A
 // column of a head's memory lies together in the state table, so a warp reads and writes whole lines.
@@ -156,34 +156,40 @@ __device__ __forceinline__ void delta_copy16(float* dst, const float* src) {
 
 // R: memory rows a lane holds (d <= 32 R); CH: rows of the step staged at a time. The rows' inputs (k, q, the block's
 // values, decay, step size, q.k) come into shared memory a chunk at a time by asynchronous copies, the next chunk
-// while this one is walked: a row's step then waits for shared memory only.
-template <int R, int CH>
+// while this one is walked: a row's step then waits for shared memory only. A warp holds DW columns of the memory,
+// so k and q are read once for all of them and the 2 DW dot products of a row are reduced together: each round of
+// shuffles halves the number of sums a lane carries (9 shuffles for 8 sums instead of 40).
+// DW (1, 2 or 4): columns a warp; the launcher takes the most that still leaves the GPU enough warps.
+template <int R, int CH, int DW>
 __global__ void __launch_bounds__(DC * 32)
 delta_scan_kernel(const DeltaParams p) {
+    constexpr int DCOLS = DC * DW;                              // columns a block
+    constexpr int SHIFT = DW == 4 ? 2 : (DW == 2 ? 3 : 4);     // the sum of column c ends in lane c << SHIFT (M.k) and 16 + (c << SHIFT) (M.q)
     extern __shared__ __align__(16) float staged[];             // [2][CH][rowf]
     const int entry = blockIdx.x, head = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int c = blockIdx.z * DC + warp;
+    const int c0 = blockIdx.z * DCOLS + warp * DW;              // this warp's first column
     const int r0 = p.entry_start[entry], r1 = p.entry_end[entry];
     if (r1 <= r0) return;
     const int slot = p.slots[entry];
     const int d = p.d, e = p.e;
-    const bool live = c < e;
     if (slot <= 0 || slot >= p.n_slots) {                       // rows of no request: zeros, no state
-        if (live && lane == 0)
-            for (int r = r0; r < r1; ++r) p.out[((size_t)r * p.heads + head) * e + c] = 0.f;
+        if (lane < DW && c0 + lane < e)
+            for (int r = r0; r < r1; ++r) p.out[((size_t)r * p.heads + head) * e + c0 + lane] = 0.f;
         return;
     }
     const int nq = p.kv_heads * d, nv = p.heads * e;
     const int kvh = head / (p.heads / p.kv_heads);
-    float* st = p.state + (size_t)slot * p.state_floats + (size_t)(p.taps - 1) * (2 * nq + nv) + ((size_t)head * e + (live ? c : 0)) * d;
-    float S[R];
+    float* st = p.state + (size_t)slot * p.state_floats + (size_t)(p.taps - 1) * (2 * nq + nv) + (size_t)head * e * d;
+    float S[DW][R];
 #pragma unroll
-    for (int i = 0; i < R; ++i) S[i] = (live && lane + 32 * i < d) ? st[lane + 32 * i] : 0.f;
+    for (int ci = 0; ci < DW; ++ci)
+#pragma unroll
+        for (int i = 0; i < R; ++i) S[ci][i] = (c0 + ci < e && lane + 32 * i < d) ? st[(size_t)(c0 + ci) * d + lane + 32 * i] : 0.f;
 
     constexpr int DP = R * 32;                                  // k and q padded to the lanes' rows, zeros beyond d
-    constexpr int tail = 2 * DP;                                // v [DC] | decay | step size | q.k | padding
-    constexpr int rowf = 2 * DP + 8;
+    constexpr int tail = 2 * DP;                                // v [DCOLS] | decay | step size | q.k | padding
+    constexpr int rowf = 2 * DP + DCOLS + 8;
     const bool wide = d % 4 == 0 && (((uintptr_t)p.kn | (uintptr_t)p.qn) & 15) == 0;
     auto stage = [&](int chunk, int buf) {
         const int rbase = r0 + chunk * CH;
@@ -205,16 +211,16 @@ delta_scan_kernel(const DeltaParams p) {
                 }
             }
         }
-        for (int idx = tid; idx < nr * (DC + 3); idx += DC * 32) {
-            const int t = idx / (DC + 3), x = idx - t * (DC + 3);
+        for (int idx = tid; idx < nr * (DCOLS + 3); idx += DC * 32) {
+            const int t = idx / (DCOLS + 3), x = idx - t * (DCOLS + 3);
             float* dst = base + (size_t)t * rowf + tail + x;
             const size_t r = (size_t)(rbase + t);
-            if (x < DC) {
-                const int cc = blockIdx.z * DC + x;
+            if (x < DCOLS) {
+                const int cc = blockIdx.z * DCOLS + x;
                 if (cc < e) delta_copy4(dst, p.vn + (r * p.heads + head) * e + cc);
                 else *dst = 0.f;
-            } else if (x < DC + 2) {
-                delta_copy4(dst, p.scal + (r * p.heads + head) * 2 + (x - DC));
+            } else if (x < DCOLS + 2) {
+                delta_copy4(dst, p.scal + (r * p.heads + head) * 2 + (x - DCOLS));
             } else {
                 delta_copy4(dst, p.kq + r * p.kv_heads + kvh);
             }
@@ -227,6 +233,8 @@ delta_scan_kernel(const DeltaParams p) {
             staged[(size_t)t * rowf + (x < DP - d ? d + x : DP + d + (x - (DP - d)))] = 0.f;
         }
     }
+    const bool hi16 = lane & 16, hi8 = lane & 8, hi4 = lane & 4;
+    const int mine = (lane & 15) >> SHIFT;                      // the column whose sum this lane ends up with
     const int chunks = (r1 - r0 + CH - 1) / CH;
     stage(0, 0);
     for (int ch = 0; ch < chunks; ++ch) {
@@ -242,40 +250,89 @@ delta_scan_kernel(const DeltaParams p) {
         const float* rows = staged + (size_t)(ch & 1) * CH * rowf;
         for (int t = 0; t < nr; ++t) {
             const float* in = rows + (size_t)t * rowf;
-            const float v = in[tail + warp], g = in[tail + DC], beta = in[tail + DC + 1], kq = in[tail + DC + 2];
+            const float g = in[tail + DCOLS], beta = in[tail + DCOLS + 1], kq = in[tail + DCOLS + 2];
             float k[R], q[R];
-            float a[2] = {0.f, 0.f}, b[2] = {0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < R; ++i) {
                 k[i] = in[lane + 32 * i];
                 q[i] = in[DP + lane + 32 * i];
-                S[i] *= g;
-                a[i & 1] = fmaf(S[i], k[i], a[i & 1]);
-                b[i & 1] = fmaf(S[i], q[i], b[i & 1]);
             }
-            float sa = a[0] + a[1], sb = b[0] + b[1];
+            float x[2 * DW];                                    // a lane's share of M.k for each column, then of M.q
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                sa += __shfl_xor_sync(0xffffffffu, sa, o);
-                sb += __shfl_xor_sync(0xffffffffu, sb, o);
+            for (int ci = 0; ci < DW; ++ci) {
+                float a = 0.f, b = 0.f;
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    S[ci][i] *= g;
+                    a = fmaf(S[ci][i], k[i], a);
+                    b = fmaf(S[ci][i], q[i], b);
+                }
+                x[ci] = a;
+                x[DW + ci] = b;
             }
-            const float u = beta * (v - sa);
+            // 2 DW sums over 32 lanes: each round a lane hands half of what it carries to its partner
+            float w;
+            if constexpr (DW == 4) {
+                float y[4], z[2];
 #pragma unroll
-            for (int i = 0; i < R; ++i) S[i] = fmaf(k[i], u, S[i]);
-            if (live && lane == 0) p.out[((size_t)(rbase + t) * p.heads + head) * e + c] = fmaf(u, kq, sb);
+                for (int i = 0; i < 4; ++i) {
+                    const float send = hi16 ? x[i] : x[i + 4], keep = hi16 ? x[i + 4] : x[i];
+                    y[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const float send = hi8 ? y[i] : y[i + 2], keep = hi8 ? y[i + 2] : y[i];
+                    z[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                }
+                w = (hi4 ? z[1] : z[0]) + __shfl_xor_sync(0xffffffffu, hi4 ? z[0] : z[1], 4);
+            } else if constexpr (DW == 2) {
+                float y[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const float send = hi16 ? x[i] : x[i + 2], keep = hi16 ? x[i + 2] : x[i];
+                    y[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+                }
+                w = (hi8 ? y[1] : y[0]) + __shfl_xor_sync(0xffffffffu, hi8 ? y[0] : y[1], 8);
+                w += __shfl_xor_sync(0xffffffffu, w, 4);
+            } else {
+                w = (hi16 ? x[1] : x[0]) + __shfl_xor_sync(0xffffffffu, hi16 ? x[0] : x[1], 16);
+                w += __shfl_xor_sync(0xffffffffu, w, 8);
+                w += __shfl_xor_sync(0xffffffffu, w, 4);
+            }
+            w += __shfl_xor_sync(0xffffffffu, w, 2);
+            w += __shfl_xor_sync(0xffffffffu, w, 1);
+            // lanes 0..15 now hold M.k of column (lane & 15) >> SHIFT, lanes 16..31 M.q of that column
+            float u[DW];
+#pragma unroll
+            for (int ci = 0; ci < DW; ++ci) {
+                const float a = __shfl_sync(0xffffffffu, w, ci << SHIFT);
+                u[ci] = beta * (in[tail + warp * DW + ci] - a);
+#pragma unroll
+                for (int i = 0; i < R; ++i) S[ci][i] = fmaf(k[i], u[ci], S[ci][i]);
+            }
+            if (hi16 && (lane & ((1 << SHIFT) - 1)) == 0 && c0 + mine < e) {
+                float um = u[0];
+#pragma unroll
+                for (int ci = 1; ci < DW; ++ci) um = mine == ci ? u[ci] : um;
+                p.out[((size_t)(rbase + t) * p.heads + head) * e + c0 + mine] = fmaf(um, kq, w);
+            }
         }
         __syncthreads();                                        // the chunk's buffer may be written again
     }
-    if (live) {
+#pragma unroll
+    for (int ci = 0; ci < DW; ++ci)
 #pragma unroll
         for (int i = 0; i < R; ++i)
-            if (lane + 32 * i < d) st[lane + 32 * i] = S[i];
-    }
+            if (c0 + ci < e && lane + 32 * i < d) st[(size_t)(c0 + ci) * d + lane + 32 * i] = S[ci][i];
 }
 
 }  // namespace kb
 
 using namespace kb;
+
+// 0: the launcher chooses how many columns of the memory a warp of the scan holds; 1, 2 or 4: that many (for tests and measurements).
+static int g_delta_columns = 0;
+extern "C" void kb_delta_columns_per_warp(int n) { g_delta_columns = (n == 1 || n == 2 || n == 4) ? n : 0; }
 
 // Floats a request keeps between steps: the convolutions' history, then every head's memory.
 extern "C" long long kb_delta_state_floats(int heads, int kv_heads, int d, int e, int taps) {
@@ -308,7 +365,7 @@ extern "C" int kb_delta_scan(float* out, float* scratch, const void* src, int in
     if (entries == 0 || rows == 0) return 0;
     const long long channels = 2 * nq + nv;
     KB_REQUIRE(channels * 4 <= 200 * 1024, "delta: %lld channels do not fit the shared memory of a block", channels);
-    KB_REQUIRE(heads <= 65535 && entries <= 65535 && (e + DC - 1) / DC <= 65535, "delta: too many heads, requests or value components for one launch");
+    KB_REQUIRE(heads <= 65535 && entries <= 65535 && (e + DC * 4 - 1) / (DC * 4) <= 65535, "delta: too many heads, requests or value components for one launch");
     DeltaParams p;
     p.row_width = row_width; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.b_off = b_off; p.a_off = a_off;
     p.conv = conv; p.a_log = a_log; p.dt_bias = dt_bias; p.state = state; p.state_floats = state_floats; p.row_entry = row_entry;
@@ -337,13 +394,30 @@ extern "C" int kb_delta_scan(float* out, float* scratch, const void* src, int in
     else if (in_dt == KB_DT_BF16) KB_DELTA_PREP(bf16);
     else return fail("delta: dtype code %d is not known", in_dt);
 #undef KB_DELTA_PREP
-    dim3 grid(entries, heads, (e + DC - 1) / DC);
+    // columns a warp: the most that still gives the GPU about eight warps a multiprocessor (a prompt of one request has
+    // heads x value components warps at one column each; a batch of requests has many times that)
+    int sms = 148;
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const long long columns = (long long)entries * heads * e;
+    const int dw = g_delta_columns ? g_delta_columns : (columns / 4 >= 16ll * sms ? 4 : (columns / 2 >= 8ll * sms ? 2 : 1));
+    KB_REQUIRE((e + DC * dw - 1) / (DC * dw) <= 65535, "delta: too many value components for one launch");
+    dim3 grid(entries, heads, (e + DC * dw - 1) / (DC * dw));
     const int need = (d + 31) / 32;
-#define KB_DELTA_SCAN(R, CH) delta_scan_kernel<R, CH><<<grid, DC * 32, (size_t)2 * CH * (2 * R * 32 + 8) * sizeof(float), s>>>(p)
-    if (need <= 1) KB_DELTA_SCAN(1, 16);
-    else if (need <= 2) KB_DELTA_SCAN(2, 16);
-    else if (need <= 4) KB_DELTA_SCAN(4, 16);
-    else KB_DELTA_SCAN(DELTA_R, 8);
+#define KB_DELTA_SCAN(R, CH, W) delta_scan_kernel<R, CH, W><<<grid, DC * 32, (size_t)2 * CH * (2 * R * 32 + DC * W + 8) * sizeof(float), s>>>(p)
+#define KB_DELTA_SCAN_W(R, CH)            \
+    do {                                  \
+        if (dw == 4) KB_DELTA_SCAN(R, CH, 4);      \
+        else if (dw == 2) KB_DELTA_SCAN(R, CH, 2); \
+        else KB_DELTA_SCAN(R, CH, 1);     \
+    } while (0)
+    if (need <= 1) KB_DELTA_SCAN_W(1, 16);
+    else if (need <= 2) KB_DELTA_SCAN_W(2, 16);
+    else if (need <= 4) KB_DELTA_SCAN_W(4, 16);
+    else KB_DELTA_SCAN_W(DELTA_R, 8);
+#undef KB_DELTA_SCAN_W
 #undef KB_DELTA_SCAN
     return check_launch("delta scan");
 }

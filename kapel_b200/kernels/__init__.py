@@ -65,6 +65,8 @@ def library():
                     getattr(lib, name).restype = ctypes.c_longlong
                 lib.kb_launch_count.restype = ctypes.c_ulonglong
                 lib.kb_set_pdl(1 if PDL else 0)
+                if _os.environ.get("KAPEL_B200_DELTA_COLUMNS"):      # 1, 2 or 4 columns a warp in the delta scan instead of the launcher's choice
+                    lib.kb_delta_columns_per_warp(int(_os.environ["KAPEL_B200_DELTA_COLUMNS"]))
                 _lib = lib
     return _lib
 
@@ -936,6 +938,12 @@ def delta_state_floats(heads: int, kv_heads: int, d: int, e: int, taps: int) -> 
     every convolved channel (queries, keys, values), then every head's memory [e, d]. Plain
     arithmetic (a cache is sized without the CUDA library); `delta_scan` checks it against the library's."""
     return (taps - 1) * (2 * kv_heads * d + heads * e) + heads * d * e
+
+
+def delta_columns_per_warp(n: int = 0) -> None:
+    """How many columns of a head's memory a warp of the delta scan holds: 1, 2 or 4, or 0 for the
+    launcher's own choice by the warps a step has (for tests and measurements)."""
+    library().kb_delta_columns_per_warp(int(n))
 
 
 def delta_scan(stacked, q_off: int, k_off: int, v_off: int, b_off: int, a_off: int, conv: torch.Tensor, a_log: torch.Tensor,

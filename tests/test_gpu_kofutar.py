@@ -385,10 +385,21 @@ def test_a_sink_takes_its_share_and_a_far_key_is_found(kernel):
                         assert np.abs(y[i, 0] - stored[target, :dv]).max() > 5e-2         # a row before the key does not see it
 
 
+@pytest.fixture
+def scan_columns(request):
+    from kapel_b200 import kernels as K
+
+    K.delta_columns_per_warp(request.param)
+    yield request.param
+    K.delta_columns_per_warp(0)
+
+
+@pytest.mark.parametrize("scan_columns", [0, 1, 2, 4], indirect=True)
 @pytest.mark.parametrize("H,G,d,e,taps", [(4, 2, 16, 24, 3), (1, 1, 24, 20, 1), (2, 2, 40, 8, 4), (3, 1, 130, 5, 8)])
-def test_delta_rule_in_portions_and_token_by_token_against_plain(H, G, d, e, taps):
+def test_delta_rule_in_portions_and_token_by_token_against_plain(H, G, d, e, taps, scan_columns):
     """Three requests of unequal length: whole, then in portions down to two tokens beside each other's single tokens,
-    through slots that are used again; the memory and the convolutions' history carry across steps."""
+    through slots that are used again; the memory and the convolutions' history carry across steps. With one, two
+    and four columns of the memory a warp (the launcher's own choice depends on how many warps a step has)."""
     from kapel_b200 import kernels as K
 
     rng = np.random.default_rng(d)
